@@ -33,7 +33,9 @@ class CacheNeed:
     `value_dim` where that is given and differs), all of them (window None), the last `window`, or those of the
     running chunk of `chunk` positions (a mixer whose tokens only look back to the start of their own chunk: positions
     of chunks that are over are never read again; several mixers that read one entry with chunks of their own give a
-    tuple of sizes, and a position is kept while any of them can still see it). kind "state": a float32 tensor of `state_shape` per sequence. kind
+    tuple of sizes, and a position is kept while any of them can still see it). With `keys_only` a position holds one
+    row of `head_dim` values per kv head and nothing else (a mixer whose values are made from what its keys are made
+    from). kind "state": a float32 tensor of `state_shape` per sequence. kind
     "several": a mixer that keeps more than one thing (keys and values beside a state, two states) lists them in
     `parts`; the model gives every part a cache entry of its own and hands the mixer their views in that order."""
 
@@ -45,6 +47,7 @@ class CacheNeed:
     parts: tuple["CacheNeed", ...] = ()
     value_dim: int = 0
     chunk: int | tuple[int, ...] | None = None
+    keys_only: bool = False
 
     def chunks(self) -> tuple[int, ...]:
         if not self.chunk:
@@ -56,12 +59,14 @@ class KvView:
     """What a kernel needs to address one cache entry."""
 
     __slots__ = ("base_ptr", "storage", "page_table", "max_pages", "page_size", "kv_heads", "head_dim", "dtype",
-                 "window", "value_dim")
+                 "window", "value_dim", "keys_only")
 
-    def __init__(self, storage, page_table, page_size, kv_heads, head_dim, window, value_dim=0):
+    def __init__(self, storage, page_table, page_size, kv_heads, head_dim, window, value_dim=0, keys_only=False):
         # [pages, 2, kv_heads, page_size, head_dim]; with values of another size than the keys a page is
         # [keys: kv_heads, page_size, head_dim | values: kv_heads, page_size, value_dim], stored flat
+        # (a keys-only entry's page is [kv_heads, page_size, head_dim], stored flat)
         self.storage = storage
+        self.keys_only = bool(keys_only)
         self.value_dim = value_dim or head_dim
         self.base_ptr = storage.data_ptr()
         self.page_table = page_table
@@ -83,7 +88,9 @@ class _KvGroup:
         self.storage = self.table = None
         if device is not None:
             # zeros, not garbage: a blockwise kernel multiplies masked rows of a page by probability 0
-            if need.value_dim in (0, need.head_dim):
+            if need.keys_only:
+                shape = (len(entries), n_pages, need.kv_heads * page_size * need.head_dim)
+            elif need.value_dim in (0, need.head_dim):
                 shape = (len(entries), n_pages, 2, need.kv_heads, page_size, need.head_dim)
             else:
                 shape = (len(entries), n_pages, need.kv_heads * page_size * (need.head_dim + need.value_dim))
@@ -253,7 +260,7 @@ class PagedCache:
     def kv_view(self, entry: int) -> KvView:
         group, index = self._where[entry]
         return KvView(group.storage[index], group.table, self.page_size, group.need.kv_heads, group.need.head_dim,
-                      group.need.window, group.need.value_dim)
+                      group.need.window, group.need.value_dim, group.need.keys_only)
 
     def state(self, entry: int) -> torch.Tensor:
         """The fixed-size state of entry `entry`: [slots, *state_shape] float32."""

@@ -657,3 +657,210 @@ DLLM_EXPORT int dllm_concat_restart(void* both, float* x, const float* kept, con
                            (__nv_bfloat16*)both, x, kept, start, total, hidden);
   return DLLM_BAD_ARGUMENT;
 }
+
+// ---- RMS norm followed by a short causal convolution over time ------------------------------------------------------
+// h_t = x_t / sqrt(mean(x_t^2) + eps) * w;  out_t = h_t + sum_j taps[:, j] h_(t - n_taps + 1 + j): every channel is
+// filtered over the sequence's own earlier tokens (zeros before its start), the last tap on the token itself. The
+// normed rows of tokens before the step come from `history` [slots, n_taps - 1, hidden] (float32, the oldest first),
+// those of the step are normed again here from the stream (a row's norm costs one pass over it). A block per token;
+// everything float32, rounded once to the output type. In a step of single tokens the block also moves the history
+// on; otherwise `norm_conv_history_kernel` does, after every block has read the old one.
+#define CONV_MAX_TAPS 8
+
+template <typename T>
+__global__ void __launch_bounds__(256) norm_conv_kernel(T* __restrict__ out, const float* __restrict__ x,
+                                                        const float* __restrict__ w, const float* __restrict__ taps,
+                                                        int n_taps, float* __restrict__ history,
+                                                        const int* __restrict__ tok_seq,
+                                                        const int* __restrict__ cu_seqlens,
+                                                        const int* __restrict__ slots, int hidden, float eps,
+                                                        int single) {
+  __shared__ float scratch[32];
+  __shared__ float inv[CONV_MAX_TAPS];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x, seq = tok_seq[t], local = t - cu_seqlens[seq], slot = slots[seq];
+  const int kept = n_taps - 1;
+  for (int back = 0; back < n_taps && back <= local; ++back) {  // the rows of this step: their norms
+    const float* row = x + (size_t)(t - back) * hidden;
+    float s = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) s = fmaf(row[i], row[i], s);
+    float total = block_sum(s, scratch);
+    if (threadIdx.x == 0) inv[back] = 1.0f / sqrtf(total / (float)hidden + eps);
+  }
+  __syncthreads();
+  float* old = history + (size_t)slot * kept * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float h[CONV_MAX_TAPS];  // h[j]: the input `kept - j` tokens back
+    for (int j = 0; j < n_taps; ++j) {
+      int back = kept - j;
+      h[j] = back <= local ? x[(size_t)(t - back) * hidden + i] * inv[back] * w[i]
+                           : old[(size_t)(kept - (back - local)) * hidden + i];
+    }
+    float sum = h[kept];
+    for (int j = 0; j < n_taps; ++j) sum = fmaf(taps[(size_t)i * n_taps + j], h[j], sum);
+    out[(size_t)t * hidden + i] = from_float<T>(sum);
+    if (single)
+      for (int j = 0; j < kept; ++j) old[(size_t)j * hidden + i] = h[j + 1];
+  }
+}
+
+// The history after a step of any lengths: the last n_taps - 1 normed rows of each sequence, from the step's rows
+// where it has that many and from the old history before them. A block per sequence and kept row; a thread reads
+// what it needs of the old history before the block writes (a row r only reads rows >= r).
+__global__ void __launch_bounds__(256) norm_conv_history_kernel(const float* __restrict__ x,
+                                                                const float* __restrict__ w,
+                                                                float* __restrict__ history,
+                                                                const int* __restrict__ cu_seqlens,
+                                                                const int* __restrict__ slots, int n_taps, int hidden,
+                                                                float eps) {
+  __shared__ float scratch[32];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int seq = blockIdx.x, first = cu_seqlens[seq], count = cu_seqlens[seq + 1] - first, slot = slots[seq];
+  const int kept = n_taps - 1;
+  float* old = history + (size_t)slot * kept * hidden;
+  for (int r = 0; r < kept; ++r) {  // in order: row r's source, where it is old history, is a row behind r
+    int at = count - kept + r;      // index among the step's tokens of this sequence
+    if (at >= 0) {
+      const float* row = x + (size_t)(first + at) * hidden;
+      float s = 0.f;
+      for (int i = threadIdx.x; i < hidden; i += blockDim.x) s = fmaf(row[i], row[i], s);
+      float inv = 1.0f / sqrtf(block_sum(s, scratch) / (float)hidden + eps);
+      for (int i = threadIdx.x; i < hidden; i += blockDim.x) old[(size_t)r * hidden + i] = row[i] * inv * w[i];
+    } else {
+      for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+        old[(size_t)r * hidden + i] = old[(size_t)(r + count) * hidden + i];
+    }
+  }
+}
+
+// out[tokens, hidden] = norm(x) + conv(norm(x)) as above; taps [hidden, n_taps] float32; history [slots, n_taps - 1,
+// hidden] float32 (may be null for one tap); `single`: every sequence of the step has one token.
+DLLM_EXPORT int dllm_norm_conv(void* out, const float* x, const float* w, const float* taps, int n_taps,
+                               float* history, const int* tok_seq, const int* cu_seqlens, const int* slots, int tokens,
+                               int sequences, int hidden, float eps, int single, int out_dtype, cudaStream_t stream) {
+  if (tokens <= 0) return DLLM_OK;
+  if (hidden <= 0 || n_taps < 1 || n_taps > CONV_MAX_TAPS) return DLLM_UNSUPPORTED_SIZE;
+  if (!out || !x || !w || !taps || !tok_seq || !cu_seqlens || !slots || (n_taps > 1 && !history))
+    return DLLM_BAD_ARGUMENT;
+  int threads = hidden >= 1024 ? 256 : 128;
+  int status;
+  if (out_dtype == DLLM_F32)
+    status = dllm_launch_pdl(norm_conv_kernel<float>, dim3(tokens), dim3(threads), 0, stream, (float*)out, x, w, taps,
+                             n_taps, history, tok_seq, cu_seqlens, slots, hidden, eps, single);
+  else if (out_dtype == DLLM_BF16)
+    status = dllm_launch_pdl(norm_conv_kernel<__nv_bfloat16>, dim3(tokens), dim3(threads), 0, stream,
+                             (__nv_bfloat16*)out, x, w, taps, n_taps, history, tok_seq, cu_seqlens, slots, hidden, eps,
+                             single);
+  else
+    return DLLM_BAD_ARGUMENT;
+  if (status != DLLM_OK || single || n_taps == 1) return status;
+  return dllm_launch_pdl(norm_conv_history_kernel, dim3(sequences), dim3(threads), 0, stream, x, w, history, cu_seqlens,
+                         slots, n_taps, hidden, eps);
+}
+
+// ---- bias, activation and a gate per row behind a product -----------------------------------------------------------
+// out[r, i] = act(in[r, i] + bias[i]) * (gated ? sigmoid(in[r, width]) : 1) for i < width; `in` float32 rows of
+// `stride` values (a product's float32 output: with a gate, its column `width` is the row's gate pre-activation).
+// act 0: none, 1: gelu (erf), 2: gelu (tanh form), 3: relu squared. Float32, rounded once to the output type. `out` has
+// rows of out_width >= width values; the columns behind `width` are set to zero (a padded reduction width).
+__device__ __forceinline__ float activate(float z, int kind) {
+  if (kind == 1) return 0.5f * z * (1.0f + erff(z * 0.70710678118654752440f));
+  if (kind == 2) return 0.5f * z * (1.0f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
+  if (kind == 3) { float r = fmaxf(z, 0.f); return r * r; }
+  return z;
+}
+__device__ __forceinline__ float sigmoid_f(float g) {
+  if (g >= 0.f) return 1.0f / (1.0f + expf(-g));
+  float e = expf(g);
+  return e / (1.0f + e);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) bias_act_kernel(T* __restrict__ out, const float* __restrict__ in,
+                                                       const float* __restrict__ bias, int width, int out_width,
+                                                       int stride, int kind, int gated) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const float* row = in + (size_t)blockIdx.x * stride;
+  float gate = gated ? sigmoid_f(row[width]) : 1.0f;
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < out_width; i += gridDim.y * blockDim.x) {
+    float v = 0.f;
+    if (i < width) v = activate(row[i] + (bias != nullptr ? bias[i] : 0.f), kind) * gate;
+    out[(size_t)blockIdx.x * out_width + i] = from_float<T>(v);
+  }
+}
+
+DLLM_EXPORT int dllm_bias_act(void* out, const float* in, const float* bias, int rows, int width, int out_width,
+                              int stride, int kind, int gated, int out_dtype, cudaStream_t stream) {
+  if (rows <= 0) return DLLM_OK;
+  if (width <= 0 || out_width < width || stride < width + (gated ? 1 : 0) || kind < 0 || kind > 3)
+    return DLLM_UNSUPPORTED_SIZE;
+  if (!out || !in) return DLLM_BAD_ARGUMENT;
+  dim3 grid(rows, (width + 1023) / 1024 > 64 ? 64 : (width + 1023) / 1024);
+  if (out_dtype == DLLM_F32)
+    return dllm_launch_pdl(bias_act_kernel<float>, grid, dim3(256), 0, stream, (float*)out, in, bias, width, out_width,
+                           stride, kind, gated);
+  if (out_dtype == DLLM_BF16)
+    return dllm_launch_pdl(bias_act_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, (__nv_bfloat16*)out, in, bias,
+                           width, out_width, stride, kind, gated);
+  return DLLM_BAD_ARGUMENT;
+}
+
+// residual[r, :] += row (float32): a bias behind a product that has added into the stream.
+__global__ void __launch_bounds__(256) add_row_kernel(float* __restrict__ residual, const float* __restrict__ row,
+                                                      long long total, int hidden) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x)
+    residual[i] += row[i % hidden];
+}
+
+DLLM_EXPORT int dllm_add_row(float* residual, const float* row, int rows, int hidden, cudaStream_t stream) {
+  if (rows <= 0) return DLLM_OK;
+  if (hidden <= 0 || !residual || !row) return DLLM_BAD_ARGUMENT;
+  long long total = (long long)rows * hidden;
+  int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
+  return dllm_launch_pdl(add_row_kernel, dim3(blocks), dim3(256), 0, stream, residual, row, total, hidden);
+}
+
+// ---- a token's own embedding part times an activated gate -----------------------------------------------------------
+// out[r, i] = act(z[r, i]) * table[tokens[r], offset + i] for i < width (z float32 rows of `stride` values; the table
+// in T, rows of `table_width` values); columns width .. out_width - 1 of `out` are set to zero (a reduction width
+// padded for the product that follows). A token outside the table gives a zero row and sets the status word.
+template <typename T>
+__global__ void __launch_bounds__(128) gate_embed_kernel(T* __restrict__ out, const float* __restrict__ z, int stride,
+                                                         const T* __restrict__ table, int table_width, int vocab,
+                                                         int offset, const int* __restrict__ tokens, int width,
+                                                         int out_width, int kind, int* __restrict__ status) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int r = blockIdx.x, token = tokens[r];
+  const bool ok = token >= 0 && token < vocab;
+  if (!ok && threadIdx.x == 0) *(volatile int*)status = 64;
+  for (int i = threadIdx.x; i < out_width; i += blockDim.x) {
+    float v = 0.f;
+    if (ok && i < width)
+      v = activate(z[(size_t)r * stride + i], kind) * to_float(table[(size_t)token * table_width + offset + i]);
+    out[(size_t)r * out_width + i] = from_float<T>(v);
+  }
+}
+
+DLLM_EXPORT int dllm_gate_embed(void* out, const float* z, int stride, const void* table, int table_width, int vocab,
+                                int offset, const int* tokens, int rows, int width, int out_width, int kind,
+                                int dtype, int* status, cudaStream_t stream) {
+  if (rows <= 0) return DLLM_OK;
+  if (width <= 0 || out_width < width || offset < 0 || offset + width > table_width || kind < 0 || kind > 3)
+    return DLLM_UNSUPPORTED_SIZE;
+  if (!out || !z || !table || !tokens || !status) return DLLM_BAD_ARGUMENT;
+  if (dtype == DLLM_F32)
+    return dllm_launch_pdl(gate_embed_kernel<float>, dim3(rows), dim3(128), 0, stream, (float*)out, z, stride,
+                           (const float*)table, table_width, vocab, offset, tokens, width, out_width, kind, status);
+  if (dtype == DLLM_BF16)
+    return dllm_launch_pdl(gate_embed_kernel<__nv_bfloat16>, dim3(rows), dim3(128), 0, stream, (__nv_bfloat16*)out, z,
+                           stride, (const __nv_bfloat16*)table, table_width, vocab, offset, tokens, width, out_width,
+                           kind, status);
+  return DLLM_BAD_ARGUMENT;
+}

@@ -3,9 +3,12 @@
 //
 //   moe_route:  a block per token: logits = W_r x + b in float32 from the float32 stream, `top` rounds of arg-max (the
 //               lower expert on ties), then the weights.
+//               With `all_experts` the weights are instead the chosen experts' shares of the softmax over ALL experts'
+//               logits, as they are (they do not add up to one).
 //   moe_up:     per (token, choice): the chosen expert's gate and up rows times the token's activations, then the
 //               clamped gated unit g sigmoid(alpha g) (u + shift), g = min(gate, limit), u = clamp(up, -limit, limit).
 //               Gate and up rows interleave in the stacked weight [experts, 2 ff, width].
+//   moe_up_plain: the same for experts without a gate: act(W_up[expert] h), act by kind (relu squared, gelu).
 //   moe_down:   per token: sum over its choices of weight * W_down[expert] act, stored (or added) in float32.
 //
 // A warp owns a few output values: its lanes split the reduction in 16-byte pieces (the rows' loads asked for together),
@@ -82,7 +85,7 @@ __device__ __forceinline__ float lane_dot_router<float>(const float* w, const fl
 template <typename X>
 __global__ void __launch_bounds__(WARPS * 32) moe_route_kernel(
     const X* __restrict__ x, int width, const float* __restrict__ w, const float* __restrict__ bias, int experts,
-    int top, int tokens, int* __restrict__ chosen, float* __restrict__ weights) {
+    int top, int tokens, int* __restrict__ chosen, float* __restrict__ weights, int all_experts) {
   // a block per token: its warps share the experts' logits out, warp 0 then chooses
   __shared__ float logits[MAX_EXPERTS];
   pdl_launch_dependents();
@@ -97,7 +100,14 @@ __global__ void __launch_bounds__(WARPS * 32) moe_route_kernel(
   __syncthreads();
   if (warp != 0) return;
   float kept[MAX_TOP];
-  float largest = 0.f, total = 0.f;
+  float largest = 0.f, total = 0.f, everyone = 0.f;
+  if (all_experts) {  // the softmax's denominator over every expert, before the chosen logits are struck out
+    float most = -INFINITY;
+    for (int e = lane; e < experts; e += 32) most = fmaxf(most, logits[e]);
+    most = warp_max(most);
+    for (int e = lane; e < experts; e += 32) everyone += expf(logits[e] - most);
+    everyone = warp_sum(everyone);
+  }
   for (int k = 0; k < top; ++k) {
     float best = -INFINITY;
     int where = 0x7fffffff;
@@ -122,7 +132,7 @@ __global__ void __launch_bounds__(WARPS * 32) moe_route_kernel(
     __syncwarp();
   }
   if (lane == 0)
-    for (int k = 0; k < top; ++k) weights[(size_t)t * top + k] = kept[k] / total;
+    for (int k = 0; k < top; ++k) weights[(size_t)t * top + k] = kept[k] / (all_experts ? everyone : total);
 }
 
 constexpr int UP_PER_WARP = 2;    // gated values a warp of moe_up owns (four rows of W)
@@ -154,6 +164,50 @@ __global__ void __launch_bounds__(WARPS * 32) moe_up_kernel(
     float g = fminf(lane == 0 ? sums[0] : sums[2], limit);
     float u = fminf(fmaxf(lane == 0 ? sums[1] : sums[3], -limit), limit);
     act[(size_t)a * ff + f + lane] = from_float<T>(g / (1.0f + expf(-alpha * g)) * (u + shift));
+  }
+}
+
+__device__ __forceinline__ float plain_activation(float z, int kind) {
+  if (kind == 1) return 0.5f * z * (1.0f + erff(z * 0.70710678118654752440f));
+  if (kind == 2) return 0.5f * z * (1.0f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
+  float r = fmaxf(z, 0.f);
+  return r * r;
+}
+
+constexpr int PLAIN_PER_WARP = 4;  // activated values a warp of moe_up_plain owns
+
+template <typename T>
+__global__ void __launch_bounds__(WARPS * 32) moe_up_plain_kernel(
+    T* __restrict__ act, const T* __restrict__ h, int width, const T* __restrict__ w_up, int ff, int top,
+    const int* __restrict__ chosen, int kind) {
+  pdl_launch_dependents();
+  int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int f = (blockIdx.y * WARPS + warp) * PLAIN_PER_WARP;
+  if (f >= ff) return;
+  pdl_wait();
+  int a = blockIdx.x;
+  int e = chosen[a];
+  const T* row = h + (size_t)(a / top) * width;
+  const T* w = w_up + ((size_t)e * ff + f) * width;
+  int count = min(PLAIN_PER_WARP, ff - f);
+  float sums[PLAIN_PER_WARP];
+  if (count == PLAIN_PER_WARP) {
+    lane_dots<PLAIN_PER_WARP>(w, (size_t)width, row, width, lane, sums);
+  } else {
+#pragma unroll
+    for (int r = 0; r < PLAIN_PER_WARP; ++r) {
+      sums[r] = 0.f;
+      if (r < count) lane_dots<1>(w + (size_t)r * width, (size_t)width, row, width, lane, &sums[r]);
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < PLAIN_PER_WARP; ++r) sums[r] = warp_sum(sums[r]);
+  if (lane < count) {
+    float mine = sums[0];
+#pragma unroll
+    for (int r = 1; r < PLAIN_PER_WARP; ++r)
+      if (lane == r) mine = sums[r];
+    act[(size_t)a * ff + f + lane] = from_float<T>(plain_activation(mine, kind));
   }
 }
 
@@ -201,7 +255,8 @@ __global__ void __launch_bounds__(WARPS * 32) moe_down_kernel(
 }  // namespace
 
 DLLM_EXPORT int dllm_moe_route(const void* x, int width, const float* w, const float* bias, int experts, int top,
-                               int tokens, int* chosen, float* weights, int dtype, cudaStream_t stream) {
+                               int tokens, int* chosen, float* weights, int all_experts, int dtype,
+                               cudaStream_t stream) {
   if (tokens <= 0) return DLLM_OK;
   if (experts <= 0 || experts > MAX_EXPERTS || top <= 0 || top > MAX_TOP || top > experts || width <= 0)
     return DLLM_UNSUPPORTED_SIZE;
@@ -209,10 +264,10 @@ DLLM_EXPORT int dllm_moe_route(const void* x, int width, const float* w, const f
   dim3 grid(tokens), block(WARPS * 32);
   if (dtype == DLLM_F32)
     return dllm_launch_pdl(moe_route_kernel<float>, grid, block, 0, stream, (const float*)x, width, w, bias, experts,
-                           top, tokens, chosen, weights);
+                           top, tokens, chosen, weights, all_experts);
   if (dtype == DLLM_BF16)
     return dllm_launch_pdl(moe_route_kernel<__nv_bfloat16>, grid, block, 0, stream, (const __nv_bfloat16*)x, width, w,
-                           bias, experts, top, tokens, chosen, weights);
+                           bias, experts, top, tokens, chosen, weights, all_experts);
   return DLLM_BAD_ARGUMENT;
 }
 
@@ -243,5 +298,21 @@ DLLM_EXPORT int dllm_moe_down(float* out, const void* act, int ff, const void* w
   if (dtype == DLLM_BF16)
     return dllm_launch_pdl(moe_down_kernel<__nv_bfloat16>, grid, block, 0, stream, out, (const __nv_bfloat16*)act, ff,
                            (const __nv_bfloat16*)w_down, width, top, chosen, weights, accumulate);
+  return DLLM_BAD_ARGUMENT;
+}
+
+// act[t, k] = activation(W_up[chosen[t, k]] h[t]); W_up [experts, ff, width]; kind 1: gelu (erf), 2: gelu (tanh form),
+// 3: relu squared.
+DLLM_EXPORT int dllm_moe_up_plain(void* act, const void* h, int width, const void* w_up, int ff, int top, int tokens,
+                                  const int* chosen, int kind, int dtype, cudaStream_t stream) {
+  if (tokens <= 0) return DLLM_OK;
+  if (width <= 0 || ff <= 0 || top <= 0 || ff > 65535 * WARPS || kind < 1 || kind > 3) return DLLM_UNSUPPORTED_SIZE;
+  dim3 grid(tokens * top, (ff + WARPS * PLAIN_PER_WARP - 1) / (WARPS * PLAIN_PER_WARP)), block(WARPS * 32);
+  if (dtype == DLLM_F32)
+    return dllm_launch_pdl(moe_up_plain_kernel<float>, grid, block, 0, stream, (float*)act, (const float*)h, width,
+                           (const float*)w_up, ff, top, chosen, kind);
+  if (dtype == DLLM_BF16)
+    return dllm_launch_pdl(moe_up_plain_kernel<__nv_bfloat16>, grid, block, 0, stream, (__nv_bfloat16*)act,
+                           (const __nv_bfloat16*)h, width, (const __nv_bfloat16*)w_up, ff, top, chosen, kind);
   return DLLM_BAD_ARGUMENT;
 }

@@ -3,6 +3,8 @@
 //
 //   decayed outer products:  S <- decay_h S + k_t v_t^T;                          o_t = S^T q_t
 //   gated delta rule:        S <- g_t S;  u = beta_t (v_t - S^T k_t);  S <- S + k_t u^T;  o_t = S^T q_t
+//   gated outer products:    S <- a_t S + b_t k_t v_t^T  (a_t, b_t per token and head);   o_t = S^T q_t, and the
+//                            same sum with v = 1 as one more column of S (the normaliser n_t), read out as n_t . q_t
 //
 // One kernel serves prompts and single tokens: a block owns 16 columns of one head's S for one sequence and walks
 // that sequence's new tokens in order, from the state the cache holds to the state it leaves there. A column's
@@ -60,6 +62,9 @@ struct ScanArgs {
   // gated delta rule: per token [g (heads) | beta (heads) | k.q (qk_heads)], `aux_stride` floats a token
   const float* aux;
   int aux_stride;
+  // gated outer products: aux holds per token [a (heads) | b (heads) | -]; the state has vdim + 1 columns, the last
+  // one written with v = 1, and its read-out goes to nq [tokens][heads]
+  float* nq;
 };
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
@@ -67,7 +72,7 @@ __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem) : "memory");
 }
 
-// MODE 0: decayed outer products; MODE 1: gated delta rule. TOKENS: tokens a stage. LPC lanes share a column (8 or
+// MODE 0: decayed outer products; MODE 1: gated delta rule; MODE 2: gated outer products. TOKENS: tokens a stage. LPC lanes share a column (8 or
 // 16), each with RPL rows of it: the block has 16 * LPC threads. Few lanes a column mean few shuffles and few
 // instructions a token; many lanes mean more warps to hide latency behind, which is what a step with few sequences
 // and heads needs (one warp per scheduler issues a dependent instruction every four cycles and no faster).
@@ -86,15 +91,16 @@ __global__ void __launch_bounds__(SCAN_COLS * LPC) scan_kernel(ScanArgs a) {
   const int rg = lane / CPW, cc = lane % CPW;
   const int col = col0 + warp * CPW + cc;
   const float decay = MODE == 0 ? a.decay[head] : 0.f;
+  const int state_cols = a.vdim + (MODE == 2 ? 1 : 0);
   pdl_wait();
   const int first = a.cu_seqlens[seq], count = a.cu_seqlens[seq + 1] - first;
   const int slot = a.slots[seq];
-  float* my_state = a.state + (((size_t)slot * a.heads + head) * a.vdim + col) * (size_t)a.dim + rg * RPL;
+  float* my_state = a.state + (((size_t)slot * a.heads + head) * state_cols + col) * (size_t)a.dim + rg * RPL;
 
   float S[RPL];  // (dim is a multiple of 4 and so is a lane's first row: a piece of 4 rows is inside the head or not)
 #pragma unroll
   for (int j = 0; j < RPL; j += 4) {
-    float4 s4 = (col < a.vdim && rg * RPL + j < a.dim) ? *reinterpret_cast<const float4*>(my_state + j)
+    float4 s4 = (col < state_cols && rg * RPL + j < a.dim) ? *reinterpret_cast<const float4*>(my_state + j)
                                                          : make_float4(0.f, 0.f, 0.f, 0.f);
     S[j] = s4.x; S[j + 1] = s4.y; S[j + 2] = s4.z; S[j + 3] = s4.w;
   }
@@ -119,7 +125,7 @@ __global__ void __launch_bounds__(SCAN_COLS * LPC) scan_kernel(ScanArgs a) {
           if (e - DIMP < a.dim) src = q0 + row + (e - DIMP);
         } else if (e < 2 * DIMP + SCAN_COLS) {
           if (col0 + e - 2 * DIMP < a.vdim) src = v0 + row + (e - 2 * DIMP);
-        } else if (MODE == 1) {
+        } else if (MODE >= 1) {
           const float* aux = a.aux + (size_t)(first + t0 + t) * a.aux_stride;
           cp_async4(to, aux + head);
           cp_async4(to + 1, aux + a.heads + head);
@@ -141,7 +147,7 @@ __global__ void __launch_bounds__(SCAN_COLS * LPC) scan_kernel(ScanArgs a) {
         } else if (e < 2 * DIMP + SCAN_COLS) {
           int c = col0 + e - 2 * DIMP;
           if (c < a.vdim) src = a.v + token * a.stride + head * a.vdim + c;
-        } else if (MODE == 1) {
+        } else if (MODE >= 1) {
           int which = e - 2 * DIMP - SCAN_COLS;
           if (which == 0) src = a.aux + token * a.aux_stride + head;
           else if (which == 1) src = a.aux + token * a.aux_stride + a.heads + head;
@@ -158,7 +164,12 @@ __global__ void __launch_bounds__(SCAN_COLS * LPC) scan_kernel(ScanArgs a) {
   // (the packed float32 multiply-add of sm_100: the same roundings as two single ones, half the issue slots).
   auto decayed = [&](const float* row) -> float {
     float v = row[2 * DIMP + warp * CPW + cc];
-    const float2 vv = make_float2(v, v), dd = make_float2(decay, decay);
+    float keep = decay;
+    if (MODE == 2) {  // this token's own factors; the column behind the values is written with v = 1
+      keep = row[2 * DIMP + SCAN_COLS];
+      v = (col == a.vdim ? 1.0f : v) * row[2 * DIMP + SCAN_COLS + 1];
+    }
+    const float2 vv = make_float2(v, v), dd = make_float2(keep, keep);
     float2 p = make_float2(0.f, 0.f);
 #pragma unroll
     for (int j = 0; j < RPL; j += 4) {
@@ -192,7 +203,7 @@ __global__ void __launch_bounds__(SCAN_COLS * LPC) scan_kernel(ScanArgs a) {
     float* out = a.out + (size_t)(first + chunk * TOKENS) * out_width + head * a.vdim + col;
     const bool writes = rg == 0 && col < a.vdim;
     int t = 0;
-    if (MODE == 0) {
+    if (MODE == 0 || MODE == 2) {
       // The decayed sum's read-out does not feed the state, so its sum over the rows need not be finished token by
       // token: every lane leaves its part in shared memory and goes on to the next token (nothing but the state's
       // own multiply-add links two tokens); after the chunk the block adds the parts up, a thread per token and
@@ -205,21 +216,25 @@ __global__ void __launch_bounds__(SCAN_COLS * LPC) scan_kernel(ScanArgs a) {
       int u = 0;
       for (; u + GROUP <= here; u += GROUP) {
         float4 kq[GROUP][RPL / 2];
-        float v[GROUP];
+        float v[GROUP], keep[GROUP];
 #pragma unroll
         for (int w = 0; w < GROUP; ++w) {
           const float* row = base + (u + w) * PER_TOKEN;
           v[w] = row[2 * DIMP + warp * CPW + cc];
+          keep[w] = decay;
+          if (MODE == 2) {
+            keep[w] = row[2 * DIMP + SCAN_COLS];
+            v[w] = (col == a.vdim ? 1.0f : v[w]) * row[2 * DIMP + SCAN_COLS + 1];
+          }
 #pragma unroll
           for (int j = 0; j < RPL; j += 4) {
             kq[w][j / 2] = *reinterpret_cast<const float4*>(row + rg * RPL + j);
             kq[w][j / 2 + 1] = *reinterpret_cast<const float4*>(row + DIMP + rg * RPL + j);
           }
         }
-        const float2 dd = make_float2(decay, decay);
 #pragma unroll
         for (int w = 0; w < GROUP; ++w) {
-          const float2 vv = make_float2(v[w], v[w]);
+          const float2 vv = make_float2(v[w], v[w]), dd = make_float2(keep[w], keep[w]);
           float2 p = make_float2(0.f, 0.f);
 #pragma unroll
           for (int j = 0; j < RPL; j += 4) {
@@ -247,6 +262,8 @@ __global__ void __launch_bounds__(SCAN_COLS * LPC) scan_kernel(ScanArgs a) {
         }
         if (col0 + c < a.vdim)
           a.out[(size_t)(first + chunk * TOKENS + u) * out_width + head * a.vdim + col0 + c] = sum * a.out_scale;
+        else if (MODE == 2 && col0 + c == a.vdim)
+          a.nq[(size_t)(first + chunk * TOKENS + u) * a.heads + head] = sum * a.out_scale;
       }
       t = here;
     }
@@ -292,14 +309,14 @@ __global__ void __launch_bounds__(SCAN_COLS * LPC) scan_kernel(ScanArgs a) {
   }
 #pragma unroll
   for (int j = 0; j < RPL; j += 4)
-    if (col < a.vdim && rg * RPL + j < a.dim)
+    if (col < state_cols && rg * RPL + j < a.dim)
       *reinterpret_cast<float4*>(my_state + j) = make_float4(S[j], S[j + 1], S[j + 2], S[j + 3]);
 }
 
 template <int RPL, int LPC, int MODE, int TOKENS, int STAGES>
 static int launch_scan_case(const ScanArgs& a, dim3 grid, cudaStream_t stream) {
   size_t bytes = (size_t)STAGES * TOKENS * (2 * RPL * LPC + SCAN_COLS + 4) * sizeof(float);
-  if (MODE == 0) bytes += (size_t)TOKENS * SCAN_COLS * (LPC + 4) * sizeof(float);  // the parts of the read-out
+  if (MODE != 1) bytes += (size_t)TOKENS * SCAN_COLS * (LPC + 4) * sizeof(float);  // the parts of the read-out
   static bool allowed = false;  // (more than 48 KB of dynamic shared memory has to be asked for once)
   if (bytes > 48 * 1024 && !allowed) {
     if (cudaFuncSetAttribute(scan_kernel<RPL, LPC, MODE, TOKENS, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -313,7 +330,7 @@ static int launch_scan_case(const ScanArgs& a, dim3 grid, cudaStream_t stream) {
 // `longest`: the most new tokens a sequence of the step has (the host knows; the kernel reads the real counts).
 template <int MODE>
 static int launch_scan(const ScanArgs& a, int sequences, int longest, cudaStream_t stream) {
-  dim3 grid((a.vdim + SCAN_COLS - 1) / SCAN_COLS, a.heads, sequences);
+  dim3 grid((a.vdim + (MODE == 2 ? 1 : 0) + SCAN_COLS - 1) / SCAN_COLS, a.heads, sequences);
   // Lanes a column: 8 where the step has blocks enough to give every scheduler several warps (many sequences or
   // heads), else 16, which doubles the warps (measured on one prompt of 2,048 tokens, 16 heads of 128 x 128: 477 us
   // with 8 lanes, 397 with 16, 427 with 32, whose warps each read all of k and q from shared memory again).
@@ -374,6 +391,136 @@ DLLM_EXPORT int dllm_delta_scan(const float* q, const float* k, const float* v, 
   a.state = state; a.cu_seqlens = cu_seqlens; a.slots = slots; a.out = out; a.aux = aux; a.aux_stride = aux_stride;
   a.out_scale = 1.0f; a.vector = scan_vector(q, k, v, stride, dim, vdim);
   return launch_scan<1>(a, sequences, longest, stream);
+}
+
+// Gated outer products over the new tokens of every sequence: S <- a_t S + b_t k_t v_t^T per head, out = S^T q times
+// q_scale, and the same recurrence with v = 1 in one more column of the state, whose read-out n_t . q_t (times
+// q_scale) goes to nq [tokens][heads]. aux [tokens][aux_stride] holds a (heads) then b (heads). state [slots][heads]
+// [vdim + 1][dim].
+DLLM_EXPORT int dllm_gated_scan(const float* q, const float* k, const float* v, int stride, int heads, int dim, int vdim,
+                                const float* aux, int aux_stride, float q_scale, float* state, const int* cu_seqlens,
+                                const int* slots, int sequences, int longest, float* out, float* nq,
+                                cudaStream_t stream) {
+  if (sequences <= 0) return DLLM_OK;
+  if (!scan_sizes_ok(heads, heads, dim, vdim, stride) || sequences >= 65536 || aux_stride < 3 * heads)
+    return DLLM_UNSUPPORTED_SIZE;
+  if (!q || !k || !v || !aux || !state || !cu_seqlens || !slots || !out || !nq) return DLLM_BAD_ARGUMENT;
+  ScanArgs a = {};
+  a.q = q; a.k = k; a.v = v; a.stride = stride; a.heads = heads; a.qk_heads = heads; a.dim = dim; a.vdim = vdim;
+  a.state = state; a.cu_seqlens = cu_seqlens; a.slots = slots; a.out = out; a.aux = aux; a.aux_stride = aux_stride;
+  a.nq = nq; a.out_scale = q_scale; a.vector = scan_vector(q, k, v, stride, dim, vdim);
+  return launch_scan<2>(a, sequences, longest, stream);
+}
+
+// ---- the gates of the gated outer products under a running maximum ------------------------------------------------
+// Per token and head, from pre-activations zi, zf (float32 columns of the projected rows) and biases: the log input
+// gate i = cap tanh((zi + bi) / cap) and the log forget gate f = logsigmoid(cap tanh((zf + bf) / cap)); with the running
+// maximum m' = max(f + m, i) (m carried per sequence and head in `m_state` [slots][heads], zero at a sequence's start):
+// aux[t] = [ a = exp(f + m - m') | b = exp(i - m') | e = exp(-m') ], each `heads` wide. A warp per (sequence, head) walks
+// the step's tokens 32 at a time: the map m -> max(m + F, I) of a token composes associatively, (F1, I1) then (F2, I2)
+// giving (F1 + F2, max(I1 + F2, I2)), so a chunk is a prefix scan over the lanes.
+__device__ __forceinline__ float log_sigmoid(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
+
+__global__ void __launch_bounds__(128) running_max_gates_kernel(
+    const float* __restrict__ zi, const float* __restrict__ zf, int stride, const float* __restrict__ bi,
+    const float* __restrict__ bf, float cap, float* __restrict__ m_state, const int* __restrict__ cu_seqlens,
+    const int* __restrict__ slots, int sequences, int heads, float* __restrict__ aux, int aux_stride) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const long long unit = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (unit >= (long long)sequences * heads) return;
+  const int seq = (int)(unit / heads), head = (int)(unit - (long long)seq * heads);
+  const int first = cu_seqlens[seq], count = cu_seqlens[seq + 1] - first;
+  float* kept = m_state + (size_t)slots[seq] * heads + head;
+  float m = *kept;
+  const float add_i = bi != nullptr ? bi[head] : 0.f, add_f = bf != nullptr ? bf[head] : 0.f;
+  for (int t0 = 0; t0 < count; t0 += 32) {
+    const int t = t0 + lane;
+    float gi = -INFINITY, gf = 0.f;  // (a lane beyond the end is the identity map)
+    if (t < count) {
+      gi = cap * tanhf((zi[(size_t)(first + t) * stride + head] + add_i) / cap);
+      gf = log_sigmoid(cap * tanhf((zf[(size_t)(first + t) * stride + head] + add_f) / cap));
+    }
+    float F = gf, I = gi;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {  // the maps of the lanes before, composed with this one
+      float pf = __shfl_up_sync(0xffffffffu, F, o), pi = __shfl_up_sync(0xffffffffu, I, o);
+      if (lane >= o) { I = fmaxf(pi + F, I); F = pf + F; }
+    }
+    float mine = fmaxf(m + F, I);
+    float before = __shfl_up_sync(0xffffffffu, mine, 1);
+    if (lane == 0) before = m;
+    if (t < count) {
+      float* dst = aux + (size_t)(first + t) * aux_stride + head;
+      dst[0] = expf(gf + before - mine);
+      dst[heads] = expf(gi - mine);
+      dst[2 * heads] = expf(-mine);
+    }
+    m = __shfl_sync(0xffffffffu, mine, min(31, count - 1 - t0));
+  }
+  if (lane == 0) *kept = m;
+}
+
+DLLM_EXPORT int dllm_running_max_gates(const float* zi, const float* zf, int stride, const float* bi, const float* bf,
+                                       float cap, float* m_state, const int* cu_seqlens, const int* slots,
+                                       int sequences, int heads, float* aux, int aux_stride, cudaStream_t stream) {
+  if (sequences <= 0) return DLLM_OK;
+  if (heads <= 0 || stride <= 0 || aux_stride < 3 * heads || !(cap > 0.f)) return DLLM_UNSUPPORTED_SIZE;
+  if (!zi || !zf || !m_state || !cu_seqlens || !slots || !aux) return DLLM_BAD_ARGUMENT;
+  long long units = (long long)sequences * heads;
+  return dllm_launch_pdl(running_max_gates_kernel, dim3((unsigned)((units + 3) / 4)), dim3(128), 0, stream, zi, zf,
+                         stride, bi, bf, cap, m_state, cu_seqlens, slots, sequences, heads, aux, aux_stride);
+}
+
+// The read-out of the gated outer products: x [tokens, heads * vdim] is divided per head by max(|nq|, floor) + 1e-6
+// (nq [tokens][heads]; floor = the e of `aux`), then by its root mean square over the head (eps), times weight
+// [heads * vdim] if given, times sigmoid(z) with z the token's gate pre-activations; rounded once to the output type.
+template <typename T>
+__global__ void __launch_bounds__(128) normalised_readout_kernel(
+    T* __restrict__ out, const float* __restrict__ x, const float* __restrict__ nq, const float* __restrict__ floor_,
+    int floor_stride, const float* __restrict__ weight, const float* __restrict__ gate, int gate_stride, int tokens,
+    int heads, int vdim, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const long long unit = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (unit >= (long long)tokens * heads) return;
+  const int t = (int)(unit / heads), h = (int)(unit - (long long)t * heads);
+  const float* row = x + ((size_t)t * heads + h) * vdim;
+  float below = fmaxf(fabsf(nq[(size_t)t * heads + h]), floor_[(size_t)t * floor_stride + h]) + 1e-6f;
+  float inv_below = 1.0f / below;
+  float ss = 0.f;
+  for (int i = lane; i < vdim; i += 32) {
+    float v = row[i] * inv_below;
+    ss = fmaf(v, v, ss);
+  }
+  ss = warp_sum(ss);
+  float inv = inv_below / sqrtf(ss / (float)vdim + eps);
+  const float* z = gate + (size_t)t * gate_stride + h * vdim;
+  for (int i = lane; i < vdim; i += 32) {
+    float value = row[i] * inv;
+    if (weight != nullptr) value *= weight[h * vdim + i];
+    out[((size_t)t * heads + h) * vdim + i] = from_float<T>(value * sigmoid_exact(z[i]));
+  }
+}
+
+DLLM_EXPORT int dllm_normalised_readout(void* out, const float* x, const float* nq, const float* floor_,
+                                        int floor_stride, const float* weight, const float* gate, int gate_stride,
+                                        int tokens, int heads, int vdim, float eps, int out_dtype,
+                                        cudaStream_t stream) {
+  if (tokens <= 0) return DLLM_OK;
+  if (heads <= 0 || vdim <= 0) return DLLM_UNSUPPORTED_SIZE;
+  if (!out || !x || !nq || !floor_ || !gate) return DLLM_BAD_ARGUMENT;
+  long long units = (long long)tokens * heads;
+  dim3 grid((unsigned)((units + 3) / 4));
+  if (out_dtype == DLLM_F32)
+    return dllm_launch_pdl(normalised_readout_kernel<float>, grid, dim3(128), 0, stream, (float*)out, x, nq, floor_,
+                           floor_stride, weight, gate, gate_stride, tokens, heads, vdim, eps);
+  if (out_dtype == DLLM_BF16)
+    return dllm_launch_pdl(normalised_readout_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream, (__nv_bfloat16*)out,
+                           x, nq, floor_, floor_stride, weight, gate, gate_stride, tokens, heads, vdim, eps);
+  return DLLM_BAD_ARGUMENT;
 }
 
 // ---- what the delta rule needs of a token before its scan --------------------------------------------------------

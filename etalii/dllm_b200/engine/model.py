@@ -66,8 +66,10 @@ class Model:
         needs = [None] * n_entries
         for entry in self.order:
             if entry.writes_cache:
-                mixer = self.blocks[entry.layer].mixer
-                needs[entry.cache] = mixer.cache_need() if hasattr(mixer, "cache_need") else None
+                # (a block whose other parts keep something too, such as a filter's history, answers for the layer)
+                block = self.blocks[entry.layer]
+                owner = block if hasattr(block, "cache_need") else block.mixer
+                needs[entry.cache] = owner.cache_need() if hasattr(owner, "cache_need") else None
         # A mixer that keeps several things (kind "several") gets a cache entry for each, numbered behind the
         # schedule's own; its view is the tuple of their views, in the order it listed them.
         several: dict[int, list[int]] = {}

@@ -39,6 +39,7 @@ SOURCES = {
     "diff_attention": "diff_attention.cu",
     "diff_attention_prefill": "diff_attention_prefill.cu",
     "diff_attention_decode": "diff_attention_decode.cu",
+    "latent_attention": "latent_attention.cu",
     "moe": "moe.cu",
     "moe_grouped": "moe_grouped.cu",
     "sampling": "sampling.cu",

@@ -51,7 +51,32 @@ _prototypes = {
         c_void_p, c_void_p, c_int, c_float, c_float, c_float, c_float, c_float, c_int, c_int, c_int, c_void_p, c_void_p,
         c_void_p],
     ("moe", "dllm_moe_route"): [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
-                                c_void_p],
+                                c_int, c_void_p],
+    ("moe", "dllm_moe_up_plain"): [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int,
+                                   c_void_p],
+    ("elementwise", "dllm_norm_conv"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                                        c_void_p, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p],
+    ("elementwise", "dllm_bias_act"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                       c_void_p],
+    ("elementwise", "dllm_add_row"): [c_void_p, c_void_p, c_int, c_int, c_void_p],
+    ("elementwise", "dllm_gate_embed"): [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_int,
+                                         c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    ("latent_attention", "dllm_latent_prepare"): [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                                                  c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                                  c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    ("latent_attention", "dllm_latent_queries"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                                  c_int, c_float, c_void_p, c_int, c_void_p],
+    ("latent_attention", "dllm_latent_attention"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                                    c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
+    ("latent_attention", "dllm_latent_values"): [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
+                                                 c_int, c_int, c_void_p],
+    ("recurrent", "dllm_gated_scan"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int,
+                                       c_float, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
+                                       c_void_p],
+    ("recurrent", "dllm_running_max_gates"): [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_void_p,
+                                              c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p],
+    ("recurrent", "dllm_normalised_readout"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                               c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
     ("moe", "dllm_moe_up"): [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_float, c_float,
                              c_float, c_int, c_void_p],
     ("moe", "dllm_moe_down"): [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
@@ -433,9 +458,10 @@ def diff_attention_prefill(out: torch.Tensor, q: torch.Tensor, gates: torch.Tens
 
 
 def moe_route(chosen: torch.Tensor, weights: torch.Tensor, x: torch.Tensor, router: torch.Tensor,
-              bias: torch.Tensor | None, top: int) -> None:
+              bias: torch.Tensor | None, top: int, all_experts: bool = False) -> None:
     """Per row of x (float32, or the activations in bfloat16): logits = router x + bias in float32; chosen[t] = the `top` experts with the largest
-    logits, largest first (the lower expert on ties); weights[t] = the softmax over those logits only."""
+    logits, largest first (the lower expert on ties); weights[t] = the softmax over those logits only, or with
+    `all_experts` the chosen experts' shares of the softmax over every expert's logit, as they are."""
     _cuda(chosen, weights, x, router, bias)
     tokens, width = x.shape
     experts = router.shape[0]
@@ -445,7 +471,8 @@ def moe_route(chosen: torch.Tensor, weights: torch.Tensor, x: torch.Tensor, rout
     assert chosen.numel() >= tokens * top and weights.numel() >= tokens * top
     _check(_fn("moe", "dllm_moe_route")(x.data_ptr(), width, router.data_ptr(),
                                         bias.data_ptr() if bias is not None else None, experts, int(top), tokens,
-                                        chosen.data_ptr(), weights.data_ptr(), _code(x.dtype), _stream()), "moe_route",
+                                        chosen.data_ptr(), weights.data_ptr(), 1 if all_experts else 0,
+                                        _code(x.dtype), _stream()), "moe_route",
            lambda: f"experts={experts} (at most 256), top={top} (at most 16 and at most experts)")
 
 
@@ -461,6 +488,215 @@ def moe_up(act: torch.Tensor, h: torch.Tensor, w_gate_up: torch.Tensor, chosen: 
     _check(_fn("moe", "dllm_moe_up")(act.data_ptr(), h.data_ptr(), width, w_gate_up.data_ptr(), ff, int(top), tokens,
                                      chosen.data_ptr(), float(limit), float(alpha), float(shift), _code(h.dtype),
                                      _stream()), "moe_up")
+
+
+ACT_NONE, ACT_GELU, ACT_GELU_TANH, ACT_RELU_SQUARED = 0, 1, 2, 3
+ACTIVATIONS = {None: ACT_NONE, "gelu": ACT_GELU, "gelu_tanh": ACT_GELU_TANH, "relu_squared": ACT_RELU_SQUARED}
+"""The activations the pointwise kernels know, by name: the exact (erf) gelu, its tanh form 0.5 z (1 + tanh(sqrt(2/pi)
+(z + 0.044715 z^3))), and the square of relu."""
+
+
+def moe_up_plain(act: torch.Tensor, h: torch.Tensor, w_up: torch.Tensor, chosen: torch.Tensor, top: int,
+                 activation: int) -> None:
+    """act[t, k] = activation(W[chosen[t, k]] h[t]) for every token and choice: experts without a gate, W [experts,
+    ff, width]; the activation (ACT_GELU, ACT_GELU_TANH or ACT_RELU_SQUARED) in float32."""
+    _cuda(act, h, w_up, chosen)
+    tokens, width = h.shape
+    ff = w_up.shape[1]
+    assert h.dtype == w_up.dtype == act.dtype and w_up.shape[2] == width and chosen.dtype == torch.int32
+    assert act.numel() >= tokens * top * ff and chosen.numel() >= tokens * top
+    _check(_fn("moe", "dllm_moe_up_plain")(act.data_ptr(), h.data_ptr(), width, w_up.data_ptr(), ff, int(top), tokens,
+                                           chosen.data_ptr(), int(activation), _code(h.dtype), _stream()),
+           "moe_up_plain")
+
+
+def moe_plain_grouped_built() -> bool:
+    """Whether the grouped tile products know experts without a gate matrix (not yet: the per-token kernels run)."""
+    return False
+
+
+def norm_conv(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, taps: torch.Tensor,
+              history: torch.Tensor | None, eps: float, batch) -> None:
+    """out = h + conv(h) with h = x / rms(x) * weight: every channel of the normed rows is filtered over time inside
+    its own sequence, conv(h)_t = sum_j taps[:, j] h_(t - n + 1 + j) (taps [hidden, n] float32, the last column on the
+    token itself, zeros before a sequence's start). `history` [slots, n - 1, hidden] float32 holds the normed rows of
+    the tokens before the step and is moved on. x float32 [tokens, hidden]; out in either type."""
+    _cuda(out, x, weight, taps, history)
+    tokens, hidden = batch.n_tokens, x.shape[1]
+    n_taps = taps.shape[1]
+    assert x.dtype == torch.float32 and weight.dtype == torch.float32 and taps.dtype == torch.float32
+    assert weight.numel() == hidden and taps.shape[0] == hidden and out.shape[1] == hidden
+    assert x.shape[0] >= tokens and out.shape[0] >= tokens
+    assert n_taps == 1 or (history is not None and history.dtype == torch.float32 and
+                           tuple(history.shape[1:]) == (n_taps - 1, hidden))
+    _check(_fn("elementwise", "dllm_norm_conv")(
+        out.data_ptr(), x.data_ptr(), weight.data_ptr(), taps.data_ptr(), n_taps,
+        history.data_ptr() if history is not None else None, batch.tok_seq.data_ptr(), batch.cu_seqlens.data_ptr(),
+        batch.slots.data_ptr(), tokens, batch.n_seqs, hidden, float(eps), 1 if batch.is_decode else 0,
+        _code(out.dtype), _stream()), "norm_conv", lambda: f"taps={n_taps} (at most 8)")
+    if not batch.is_decode and n_taps > 1:
+        global launches
+        launches += 1  # (the history's own small kernel)
+
+
+def bias_act(out: torch.Tensor, rows: torch.Tensor, bias: torch.Tensor | None, activation: int, width: int,
+             gated: bool = False) -> None:
+    """out[r, i] = activation(rows[r, i] + bias[i]) for i < width, times sigmoid(rows[r, width]) if `gated` (the
+    column behind the activated ones is then the row's gate); out's columns behind `width` are set to zero. rows
+    float32 (a product's output); out either type."""
+    _cuda(out, rows, bias)
+    n = out.shape[0]
+    assert out.shape[1] >= width
+    assert rows.dtype == torch.float32 and rows.shape[0] >= n and rows.shape[1] >= width + (1 if gated else 0)
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == width)
+    _check(_fn("elementwise", "dllm_bias_act")(out.data_ptr(), rows.data_ptr(),
+                                               bias.data_ptr() if bias is not None else None, n, int(width),
+                                               out.shape[1], rows.shape[1],
+                                               int(activation), 1 if gated else 0, _code(out.dtype), _stream()),
+           "bias_act")
+
+
+def add_row(residual: torch.Tensor, row: torch.Tensor) -> None:
+    """residual[r] += row for every r (float32): a bias behind a product that added into the stream."""
+    _cuda(residual, row)
+    assert residual.dtype == torch.float32 and row.dtype == torch.float32 and row.numel() == residual.shape[1]
+    _check(_fn("elementwise", "dllm_add_row")(residual.data_ptr(), row.data_ptr(), residual.shape[0],
+                                              residual.shape[1], _stream()), "add_row")
+
+
+def gate_embed(out: torch.Tensor, z: torch.Tensor, table: torch.Tensor, offset: int, width: int, tokens: torch.Tensor,
+               activation: int, status: torch.Tensor | None = None) -> None:
+    """out[r, i] = activation(z[r, i]) * table[tokens[r], offset + i] for i < width, zeros in out's columns behind (a
+    reduction width padded for the next product). z float32 [rows, >= width]; table and out in the same type."""
+    _cuda(out, z, table, tokens)
+    if status is None:
+        status = _status_word()
+    rows = out.shape[0]
+    assert z.dtype == torch.float32 and z.shape[0] >= rows and z.shape[1] >= width and out.shape[1] >= width
+    assert table.dtype == out.dtype and tokens.dtype == torch.int32 and tokens.numel() >= rows
+    _check(_fn("elementwise", "dllm_gate_embed")(out.data_ptr(), z.data_ptr(), z.shape[1], table.data_ptr(),
+                                                 table.shape[1], table.shape[0], int(offset), tokens.data_ptr(), rows,
+                                                 int(width), out.shape[1], int(activation), _code(out.dtype),
+                                                 status.data_ptr(), _stream()), "gate_embed")
+
+
+def latent_prepare(rows: torch.Tensor, cq_at: int, q_rank: int, c_at: int, rank: int, rot: int,
+                   q_weight: torch.Tensor | None, c_weight: torch.Tensor, eps: float, table: torch.Tensor | None,
+                   cq_out: torch.Tensor | None, cache, batch, write_cache: bool = True) -> None:
+    """From a token's projected float32 row: the query latent (q_rank values at column cq_at) divided by its root mean
+    square times q_weight -> cq_out (activation type); the key latent (rank values at c_at) normed likewise with
+    c_weight and the `rot` values behind it rotated in halves by the token's position -> the token's row [rank + rot]
+    of the keys-only cache entry."""
+    _cuda(rows, q_weight, c_weight, table, cq_out)
+    tokens = batch.n_tokens
+    assert rows.dtype == torch.float32 and c_weight.dtype == torch.float32 and cache.head_dim == rank + rot
+    assert cache.keys_only and cache.kv_heads == 1
+    assert q_rank == 0 or (cq_out.dtype == cache.dtype and q_weight.numel() == q_rank)
+    if rot:
+        assert table.dtype == torch.float32 and table.shape[0] > batch.max_position, "position beyond the table"
+        assert table.shape[1] == rot // 2 and table.shape[2] == 2
+    _check(_fn("latent_attention", "dllm_latent_prepare")(
+        rows.data_ptr(), rows.shape[1], int(cq_at), int(q_rank), int(c_at), int(rank), int(rot),
+        q_weight.data_ptr() if q_weight is not None else None, c_weight.data_ptr(), float(eps),
+        table.data_ptr() if table is not None else None, cq_out.data_ptr() if cq_out is not None else None,
+        cache.base_ptr, cache.page_table.data_ptr(), cache.max_pages, cache.page_size, batch.tok_seq.data_ptr(),
+        batch.tok_pos.data_ptr(), batch.slots.data_ptr(), tokens, 1 if write_cache else 0, _code(cache.dtype),
+        _stream()), "latent_prepare")
+
+
+def latent_queries(out: torch.Tensor, q: torch.Tensor, uk: torch.Tensor, table: torch.Tensor | None, heads: int,
+                   dim: int, rot: int, rank: int, scale: float, batch) -> None:
+    """Queries in the latent's coordinates: q float32 [tokens, heads x (dim + rot)] head by head [plain | rotated
+    part]; out float32 [tokens, heads x (rank + rot)] = [uk_h^T q_plain | rotate(q_rot)] x scale, uk [heads x dim,
+    rank] the map from the latent to the heads' keys."""
+    _cuda(out, q, uk, table)
+    tokens = batch.n_tokens
+    assert q.dtype == torch.float32 and out.dtype == torch.float32
+    assert q.shape[1] == heads * (dim + rot) and out.shape[1] == heads * (rank + rot)
+    assert tuple(uk.shape) == (heads * dim, rank)
+    _check(_fn("latent_attention", "dllm_latent_queries")(
+        q.data_ptr(), uk.data_ptr(), table.data_ptr() if table is not None else None, out.data_ptr(), tokens, heads,
+        dim, rot, rank, float(scale), batch.tok_pos.data_ptr(), _code(uk.dtype), _stream()), "latent_queries")
+
+
+def latent_attention(out: torch.Tensor, q: torch.Tensor, cache, heads: int, rank: int, rot: int, batch) -> None:
+    """Causal softmax attention of every (token, head) over the rows [rank + rot] its sequence has cached: scores
+    q . row (the queries carry the scale), out float32 [tokens, heads x rank] = the weighted sum of the rows' first
+    `rank` values. The general kernel: float32 arithmetic, either cache type, rank up to 512."""
+    _cuda(out, q)
+    assert q.dtype == torch.float32 and out.dtype == torch.float32 and cache.head_dim == rank + rot
+    assert q.shape[1] == heads * (rank + rot) and out.shape[1] == heads * rank
+    _check(_fn("latent_attention", "dllm_latent_attention")(
+        q.data_ptr(), out.data_ptr(), cache.base_ptr, cache.page_table.data_ptr(), cache.max_pages, cache.page_size,
+        heads, rank, rot, batch.tok_seq.data_ptr(), batch.tok_pos.data_ptr(), batch.slots.data_ptr(), batch.n_tokens,
+        _code(cache.dtype), _stream()), "latent_attention", lambda: f"rank={rank} (at most 512)")
+
+
+def latent_values(out: torch.Tensor, mixed: torch.Tensor, uv: torch.Tensor, gates: torch.Tensor | None, gate_at: int,
+                  heads: int, rank: int, vdim: int) -> None:
+    """out[t, h] = (uv_h mixed[t, h]) x sigmoid(gates[t, gate_at + h]): the heads' values from their weighted sums of
+    the latent; mixed float32 [tokens, heads x rank], uv [heads x vdim, rank], out [tokens, heads x vdim] in uv's
+    type; gates float32 rows (None: no gate)."""
+    _cuda(out, mixed, uv, gates)
+    tokens = out.shape[0]
+    assert mixed.dtype == torch.float32 and out.dtype == uv.dtype and tuple(uv.shape) == (heads * vdim, rank)
+    assert mixed.shape[1] == heads * rank and out.shape[1] == heads * vdim
+    gate_ptr = (gates.data_ptr() + 4 * int(gate_at)) if gates is not None else None
+    _check(_fn("latent_attention", "dllm_latent_values")(
+        mixed.data_ptr(), uv.data_ptr(), gate_ptr, gates.shape[1] if gates is not None else 0, out.data_ptr(), tokens,
+        heads, rank, vdim, _code(out.dtype), _stream()), "latent_values")
+
+
+def latent_tiles(dtype, rank: int, rot: int):
+    """The tile shape of the tensor-core kernels for a latent of these sizes, or None where only the general kernel
+    runs (float32, or sizes the tiles do not take). No tensor-core kernel is built yet: always None."""
+    return None
+
+
+def running_max_gates(aux: torch.Tensor, rows: torch.Tensor, i_at: int, f_at: int, i_bias: torch.Tensor | None,
+                      f_bias: torch.Tensor | None, cap: float, heads: int, state: torch.Tensor, batch) -> None:
+    """The per-token factors of the gated outer products: log input gate i = cap tanh((z_i + b_i) / cap), log forget
+    gate f = logsigmoid(cap tanh((z_f + b_f) / cap)), running maximum m' = max(f + m, i) carried in `state` [slots,
+    heads] from step to step (zero at a sequence's start); aux [tokens, 3 heads] = [exp(f + m - m') | exp(i - m') |
+    exp(-m')]. z_i, z_f: columns i_at, f_at of `rows` (float32)."""
+    _cuda(aux, rows, i_bias, f_bias, state)
+    assert all(t.dtype == torch.float32 for t in (aux, rows, state)) and aux.shape[1] >= 3 * heads
+    assert tuple(state.shape[1:]) == (heads,) and aux.shape[0] >= batch.n_tokens
+    _check(_fn("recurrent", "dllm_running_max_gates")(
+        _columns(rows, i_at), _columns(rows, f_at), rows.shape[1], i_bias.data_ptr() if i_bias is not None else None,
+        f_bias.data_ptr() if f_bias is not None else None, float(cap), state.data_ptr(), batch.cu_seqlens.data_ptr(),
+        batch.slots.data_ptr(), batch.n_seqs, heads, aux.data_ptr(), aux.shape[1], _stream()), "running_max_gates")
+
+
+def gated_scan(out: torch.Tensor, nq: torch.Tensor, rows: torch.Tensor, q_at: int, k_at: int, v_at: int, heads: int,
+               dim: int, vdim: int, aux: torch.Tensor, q_scale: float, state: torch.Tensor, batch) -> None:
+    """Per sequence and head, over the step's tokens in order: S <- a_t S + b_t k v^T, out = S^T q x q_scale, and the
+    same with v = 1 in one more column of S, read out as nq [tokens, heads] = n . q x q_scale. a_t, b_t: the first
+    two blocks of `aux` (`running_max_gates`). state [slots, heads, vdim + 1, dim] float32."""
+    _cuda(out, nq, rows, aux, state)
+    assert all(t.dtype == torch.float32 for t in (out, nq, rows, aux, state))
+    assert tuple(state.shape[1:]) == (heads, vdim + 1, dim) and out.shape[1] == heads * vdim and nq.shape[1] == heads
+    _check(_fn("recurrent", "dllm_gated_scan")(
+        _columns(rows, q_at), _columns(rows, k_at), _columns(rows, v_at), rows.shape[1], heads, dim, vdim,
+        aux.data_ptr(), aux.shape[1], float(q_scale), state.data_ptr(), batch.cu_seqlens.data_ptr(),
+        batch.slots.data_ptr(), batch.n_seqs, int(batch.max_new), out.data_ptr(), nq.data_ptr(), _stream()),
+        "gated_scan", lambda: f"dim={dim} (a multiple of 4, at most 256)")
+
+
+def normalised_readout(out: torch.Tensor, x: torch.Tensor, nq: torch.Tensor, aux: torch.Tensor, floor_at: int,
+                       weight: torch.Tensor | None, rows: torch.Tensor, gate_at: int, heads: int, vdim: int,
+                       eps: float) -> None:
+    """out = x / (max(|nq|, floor) + 1e-6) per head (floor: column floor_at + head of `aux`), then divided by its
+    root mean square over the head, times weight [heads x vdim], times sigmoid of the gate pre-activations at column
+    gate_at of `rows`; x float32 [tokens, heads x vdim]."""
+    _cuda(out, x, nq, aux, weight, rows)
+    tokens = out.shape[0]
+    assert all(t.dtype == torch.float32 for t in (x, nq, aux, rows)) and x.shape[1] == heads * vdim
+    assert weight is None or (weight.dtype == torch.float32 and weight.numel() == heads * vdim)
+    _check(_fn("recurrent", "dllm_normalised_readout")(
+        out.data_ptr(), x.data_ptr(), nq.data_ptr(), _columns(aux, floor_at), aux.shape[1],
+        weight.data_ptr() if weight is not None else None, _columns(rows, gate_at), rows.shape[1], tokens, heads, vdim,
+        float(eps), _code(out.dtype), _stream()), "normalised_readout")
 
 
 def moe_down(out: torch.Tensor, act: torch.Tensor, w_down: torch.Tensor, chosen: torch.Tensor, weights: torch.Tensor,

@@ -1,4 +1,4 @@
-from . import (attention, block, differential_attention, embedding, feed_forward, linear_attention, mixture, norm,  # noqa: F401
-               parallel, position, reentry)  # (register the built-in parts)
+from . import (attention, block, differential_attention, embedding, feed_forward, latent_attention,  # noqa: F401
+               linear_attention, mixture, norm, parallel, position, reentry, short_conv, token_input)  # (register the built-in parts)
 from .registry import build_part, part_factory, register_part, unregister_part  # noqa: F401
 from .spec import LayerSpec, ModelSpec, ParamSpec, PartSpec, ScheduleEntry  # noqa: F401

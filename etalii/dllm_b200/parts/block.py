@@ -4,7 +4,9 @@ in `forward(x, batch, cache, rt, write_cache)` on the float32 residual stream x.
 
 "pre_norm": x += mixer(norm(x)); x += feed_forward(norm(x)) (reference: src/etalii_dllm/transformer.py:493-558).
 "output_norm": x += norm(mixer(x)); x += norm(feed_forward(x)): the sublayers read the stream itself and the norm sits
-on what they return."""
+on what they return.
+"filtered_pre_norm": x += mixer(filter(norm(x))); x += feed_forward(norm(x)); x += token_input(x): a filter over time
+sits between the first norm and the mixer; the feed-forward and the token input are optional."""
 from __future__ import annotations
 
 import torch
@@ -112,7 +114,55 @@ class OutputNormMixerBlock:
         add_normed_output(self.mixer_norm, x, out, rt)
 
 
+class FilteredPreNormBlock:
+    """x += mixer(filter(mixer_norm(x))); then, where the layer has them, x += feed_forward(feed_forward_norm(x)) and
+    x += token_input(x). The filter (a short convolution over time) keeps a history of its own beside what the mixer
+    keeps: the block answers for the layer's cache need and hands each part its view."""
+
+    PARTS = {"mixer": "mixer", "mixer_norm": "norm", "mixer_filter": "filter"}
+    OPTIONAL_PARTS = {"feed_forward": "feed_forward", "feed_forward_norm": "norm", "token_input": "token_input"}
+
+    def __init__(self, mixer, mixer_norm, mixer_filter, feed_forward=None, feed_forward_norm=None,
+                 token_input=None) -> None:
+        if (feed_forward is None) != (feed_forward_norm is None):
+            raise ValueError("a feed-forward and its norm come together")
+        self.mixer, self.mixer_norm, self.mixer_filter = mixer, mixer_norm, mixer_filter
+        self.feed_forward, self.feed_forward_norm, self.token_input = feed_forward, feed_forward_norm, token_input
+        self.parts = {name: part for name, part in (
+            ("mixer", mixer), ("mixer_norm", mixer_norm), ("mixer_filter", mixer_filter),
+            ("feed_forward", feed_forward), ("feed_forward_norm", feed_forward_norm), ("token_input", token_input))
+            if part is not None}
+        if feed_forward is not None and hasattr(feed_forward_norm, "give_weight_to"):
+            feed_forward_norm.give_weight_to(feed_forward)
+        self._filter_keeps = mixer_filter.cache_need() is not None
+        self._mixer_keeps = hasattr(mixer, "cache_need") and mixer.cache_need() is not None
+
+    def cache_need(self):
+        from ..cache.paged import CacheNeed
+
+        needs = []
+        if self._mixer_keeps:
+            needs.append(self.mixer.cache_need())
+        if self._filter_keeps:
+            needs.append(self.mixer_filter.cache_need())
+        if not needs:
+            return None
+        return CacheNeed("several", parts=tuple(needs))
+
+    def forward(self, x, batch, cache, rt, write_cache: bool = True) -> None:
+        views = list(cache) if cache is not None else []
+        mixer_view = views.pop(0) if self._mixer_keeps else None
+        history = views.pop(0) if self._filter_keeps else None
+        h = self.mixer_filter.forward(self.mixer_norm, x, batch, history, rt)
+        self.mixer.forward(h, x, batch, mixer_view, rt, write_cache)
+        if self.feed_forward is not None:
+            self.feed_forward.forward(normed(self.feed_forward_norm, self.feed_forward, x, rt), x, batch, rt)
+        if self.token_input is not None:
+            self.token_input.forward(x, batch, rt)
+
+
 register_part("block", "pre_norm", PreNormBlock)
+register_part("block", "filtered_pre_norm", FilteredPreNormBlock)
 register_part("block", "output_norm", OutputNormBlock)
 register_part("block", "output_norm_mixer", OutputNormMixerBlock)
 register_part("block", "pre_norm_mixer", PreNormMixerBlock)

@@ -118,5 +118,67 @@ class ClampedGLU:
         return {"gemv", "gemv_cluster", "gemm_tcgen05", "elementwise"}
 
 
+class ActivationMLP:
+    """A feed-forward without a gate matrix: down(act(up(h) + b_up)) + b_down, the activation by name ("gelu": the exact
+    erf form, "gelu_tanh", "relu_squared"), the biases optional. With `token_gate` the output is multiplied by
+    sigmoid(w_g . h), one number per token: the gate's row rides as one more row of the up matrix and multiplies the
+    activated values, which the down product is linear in. Bias, activation and gate are one float32 kernel between
+    the two products."""
+
+    def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "gelu", biases: bool = False,
+                 token_gate: bool = False) -> None:
+        self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
+        if ops.ACTIVATIONS.get(activation, 0) == 0:
+            raise ValueError(f"activation {activation!r} is not known (gelu, gelu_tanh, relu_squared)")
+        self.activation, self.biases, self.token_gate = activation, bool(biases), bool(token_gate)
+        self.padded = -(-self.intermediate_size // 8) * 8  # (the down product reads rows in 16-byte pieces)
+        self.w_up = self.w_down = self.b_up = self.b_down = None
+
+    @staticmethod
+    def parameters(hidden_size, intermediate_size, biases=False, token_gate=False, **_) -> dict[str, ParamSpec]:
+        out = {"up": ParamSpec((int(intermediate_size), hidden_size)),
+               "down": ParamSpec((hidden_size, int(intermediate_size)))}
+        if biases:
+            out.update({"up_bias": ParamSpec((int(intermediate_size),)), "down_bias": ParamSpec((hidden_size,))})
+        if token_gate:
+            out["gate"] = ParamSpec((1, hidden_size))
+        return out
+
+    def supports(self, rt) -> str | None:
+        return row_rule(rt, hidden_size=self.hidden_size)
+
+    def bind(self, tensors, rt) -> None:
+        up = tensors["up"].to(rt.dtype)
+        if self.token_gate:
+            up = torch.cat([up, tensors["gate"].to(rt.dtype).reshape(1, self.hidden_size)], dim=0)
+        self.w_up = up.contiguous().to(rt.device)
+        down = torch.zeros(self.hidden_size, self.padded, dtype=rt.dtype)
+        down[:, :self.intermediate_size] = tensors["down"].to(rt.dtype)
+        self.w_down = down.contiguous().to(rt.device)
+        if self.biases:
+            self.b_up = rt.to_device(tensors["up_bias"], torch.float32)
+            self.b_down = rt.to_device(tensors["down_bias"], torch.float32)
+
+    def forward(self, h: torch.Tensor, residual: torch.Tensor, batch, rt, epilogue: int = ops.EPI_RESIDUAL) -> None:
+        """Adds into `residual` (float32), or with `epilogue=ops.EPI_STORE_F32` writes it."""
+        if isinstance(h, NormedInput):
+            h = h.tensor()
+        rows = h.shape[0]
+        ff = self.intermediate_size
+        pre = rt.ws.buffer("ffn_pre", (rows, self.w_up.shape[0]), torch.float32)
+        ops.gemm(pre, h, self.w_up, ops.EPI_STORE_F32)
+        act = rt.ws.buffer("ffn_act", (rows, self.padded), rt.dtype)
+        ops.bias_act(act, pre, self.b_up, ops.ACTIVATIONS[self.activation], ff, self.token_gate)
+        ops.gemm(residual, act, self.w_down, epilogue)
+        if self.b_down is not None:
+            ops.add_row(residual, self.b_down)
+
+    def kernel_libraries(self, rt) -> set[str]:
+        if rt.dtype != torch.bfloat16:
+            return {"gemm_simt", "elementwise"}
+        return {"gemv", "gemv_cluster", "gemm_tcgen05", "elementwise"}
+
+
 register_part("feed_forward", "swiglu", SwiGLU)
+register_part("feed_forward", "activation_mlp", ActivationMLP)
 register_part("feed_forward", "clamped_glu", ClampedGLU)

@@ -1,0 +1,120 @@
+"""Attention whose keys and values are made from a small latent per position instead of being kept themselves.
+
+Per token, from the mixer's input h: the query goes through a latent of its own, c_q = rms(W_dq h) * w_q, q = W_uq c_q,
+laid out head by head as [dim plain | rot_dim rotated]. W_dkv h gives kv_rank + rot_dim numbers: the first kv_rank,
+divided by their root mean square and weighted, are the latent c; the last rot_dim, rotated by the position (pairs
+i, i + rot_dim / 2), are ONE key part r that all heads share. Head a has the keys [W_uk,a c | r] and the values
+W_uv,a c; the score is (q_plain . W_uk,a c + q_rot . r) * scale, causal, ordinary softmax; the head's output is
+multiplied by sigmoid(W_g h)_a and W_o runs over the concatenated heads.
+
+Only [c | r] is cached, one row per position for all heads (a keys-only cache entry). The kernels never build the
+heads' keys and values: since q_plain . W_uk c = (W_uk^T q_plain) . c, a query is taken into the latent's coordinates
+once and attention runs over the cached rows themselves, every head against the same rows; the weighted sum of c is
+then mapped through W_uv. Norms, rotation, scores, softmax and the gate are float32; the cache holds the activation
+type."""
+from __future__ import annotations
+
+import torch
+
+from ..cache.paged import CacheNeed
+from ..kernels import ops
+from .norm import row_rule
+from .registry import build_part, register_part
+from .spec import ParamSpec
+
+
+class LatentAttention:
+    def __init__(self, hidden_size: int, num_heads: int, dim: int, rot_dim: int, vdim: int, q_rank: int, kv_rank: int,
+                 scale: float, eps: float, position=None, gate: bool = True) -> None:
+        self.hidden_size, self.num_heads = int(hidden_size), int(num_heads)
+        self.dim, self.rot_dim, self.vdim = int(dim), int(rot_dim), int(vdim)
+        self.q_rank, self.kv_rank = int(q_rank), int(kv_rank)
+        self.scale, self.eps, self.gate = float(scale), float(eps), bool(gate)
+        if self.rot_dim and position is None:
+            raise ValueError("a rotated key part needs a position encoding")
+        self.position = build_part("position", position) if position is not None and self.rot_dim else None
+        if self.position is not None and self.position.rotary_dim != self.rot_dim:
+            raise ValueError(f"the position encoding turns {self.position.rotary_dim} values, the rotated part has "
+                             f"{self.rot_dim}")
+        self.w_down = self.w_uq = self.w_uk = self.w_uv = self.w_o = self.q_weight = self.c_weight = None
+
+    @staticmethod
+    def parameters(hidden_size, num_heads, dim, rot_dim, vdim, q_rank, kv_rank, gate=True, **_) -> dict[str, ParamSpec]:
+        heads = int(num_heads)
+        out = {"dq": ParamSpec((int(q_rank), hidden_size)), "dq_norm": ParamSpec((int(q_rank),), "ones"),
+               "uq": ParamSpec((heads * (int(dim) + int(rot_dim)), int(q_rank))),
+               "dkv": ParamSpec((int(kv_rank) + int(rot_dim), hidden_size)),
+               "dkv_norm": ParamSpec((int(kv_rank),), "ones"),
+               "uk": ParamSpec((heads * int(dim), int(kv_rank))), "uv": ParamSpec((heads * int(vdim), int(kv_rank))),
+               "o": ParamSpec((hidden_size, heads * int(vdim)))}
+        if gate:
+            out["g"] = ParamSpec((heads, hidden_size))
+        return out
+
+    def supports(self, rt) -> str | None:
+        if self.kv_rank > 512:
+            return f"kv_rank {self.kv_rank}: the attention kernels hold a head's sum in registers, at most 512"
+        if ops.latent_tiles(rt.dtype, self.kv_rank, self.rot_dim) is None and (self.kv_rank + self.rot_dim) * 16 > 48 * 1024:
+            return f"kv_rank + rot_dim {self.kv_rank + self.rot_dim}: the general kernel keeps four queries in 48 KB"
+        return row_rule(rt, hidden_size=self.hidden_size, q_rank=self.q_rank,
+                        **{"heads x vdim": self.num_heads * self.vdim})
+
+    def cache_need(self) -> CacheNeed:
+        return CacheNeed("kv", kv_heads=1, head_dim=self.kv_rank + self.rot_dim, keys_only=True)
+
+    def bind(self, tensors, rt) -> None:
+        # one product for everything a token needs of h: the two latents (with the shared key part) and the gates
+        names = ("dq", "dkv", "g") if self.gate else ("dq", "dkv")
+        fused = torch.cat([tensors[name].to(rt.dtype) for name in names], dim=0)
+        self.w_down = fused.contiguous().to(rt.device)
+        self.w_uq = rt.to_device(tensors["uq"], rt.dtype)
+        self.w_uk = rt.to_device(tensors["uk"], rt.dtype)
+        self.w_uv = rt.to_device(tensors["uv"], rt.dtype)
+        self.w_o = rt.to_device(tensors["o"], rt.dtype)
+        self.q_weight = rt.to_device(tensors["dq_norm"], torch.float32)
+        self.c_weight = rt.to_device(tensors["dkv_norm"], torch.float32)
+        if self.position is not None:
+            self.position.bind({}, rt)
+
+    def forward(self, h: torch.Tensor, residual: torch.Tensor, batch, cache, rt, write_cache: bool = True,
+                epilogue: int = ops.EPI_RESIDUAL) -> None:
+        """h: the mixer's input [tokens, hidden] in the activation type. Adds the output to `residual` (float32), or
+        with `epilogue=ops.EPI_STORE_F32` writes it there."""
+        n = batch.n_tokens
+        heads, dim, rot, vdim, rank = self.num_heads, self.dim, self.rot_dim, self.vdim, self.kv_rank
+        rows = rt.ws.buffer("mixer_rows", (n, self.w_down.shape[0]), torch.float32)
+        ops.gemm(rows, h, self.w_down, ops.EPI_STORE_F32)
+        table = self.position.table() if self.position is not None else None
+        cq = rt.ws.buffer("latent_cq", (n, self.q_rank), rt.dtype)
+        ops.latent_prepare(rows, 0, self.q_rank, self.q_rank, rank, rot, self.q_weight, self.c_weight, self.eps, table,
+                           cq, cache, batch, write_cache)
+        q = rt.ws.buffer("latent_q", (n, heads * (dim + rot)), torch.float32)
+        ops.gemm(q, cq, self.w_uq, ops.EPI_STORE_F32)
+        gates, gate_at = (rows, self.q_rank + rank + rot) if self.gate else (None, 0)
+        attended = rt.ws.buffer("attended", (n, heads * vdim), rt.dtype)
+        tiles = ops.latent_tiles(rt.dtype, rank, rot)
+        if tiles is not None:
+            # bfloat16 on the tensor cores: queries absorbed and rounded, attention over the rows in tiles with the
+            # heads of a token as a tile's rows, the heads' values from the sums
+            q_lat = rt.ws.buffer("latent_q_abs16", (n, heads * (rank + rot)), torch.bfloat16)
+            ops.latent_queries_tiled(q_lat, q, self.w_uk, table, heads, dim, rot, rank, self.scale, batch)
+            mixed = rt.ws.buffer("latent_mixed", (n, heads * rank), torch.float32)
+            ops.latent_attention_tiled(mixed, q_lat, cache, heads, rank, rot, batch, rt.ws)
+        else:
+            q_lat = rt.ws.buffer("latent_q_abs", (n, heads * (rank + rot)), torch.float32)
+            ops.latent_queries(q_lat, q, self.w_uk, table, heads, dim, rot, rank, self.scale, batch)
+            mixed = rt.ws.buffer("latent_mixed", (n, heads * rank), torch.float32)
+            ops.latent_attention(mixed, q_lat, cache, heads, rank, rot, batch)
+        ops.latent_values(attended, mixed, self.w_uv, gates, gate_at, heads, rank, vdim)
+        ops.gemm(residual, attended, self.w_o, epilogue)
+
+    def kernel_libraries(self, rt) -> set[str]:
+        if rt.dtype != torch.bfloat16:
+            return {"gemm_simt", "elementwise", "latent_attention"}
+        names = {"gemv", "gemv_cluster", "gemm_tcgen05", "elementwise", "latent_attention"}
+        if ops.latent_tiles(rt.dtype, self.kv_rank, self.rot_dim) is not None:
+            names.add("latent_attention_tiled")
+        return names
+
+
+register_part("mixer", "latent_attention", LatentAttention)

@@ -4,7 +4,9 @@ and what the write is:
 
   "decay_linear_attention": S <- decay_h S + k v^T with a fixed decay per head (retention, lightning attention);
   "gated_delta_rule":       S <- g S; S <- S + k (beta (v - S^T k))^T with a decay g and a step size beta per token
-                            and head, q and k unit vectors after a short causal convolution over time.
+                            and head, q and k unit vectors after a short causal convolution over time;
+  "gated_matrix_memory":    S <- a_t S + b_t k v^T with exponential input gates held in range by a running maximum of the
+                            log gates, a normaliser n carried beside S, the read-out divided by max(|n . q|, e^-m).
 
 S lives in the cache's fixed-size state, one per slot and cache entry, starts at zero when a slot is taken and is
 carried from step to step; the kernels (csrc/recurrent.cu) walk a step's tokens in order, so a prompt may be cut
@@ -167,5 +169,73 @@ class GatedDeltaRule:
         return _libraries(rt)
 
 
+class GatedMatrixMemory:
+    """q = W_q h * dim^-1/2, k = W_k h [heads x dim], v = W_v h [heads x vdim]. Per head a log input gate
+    i = cap tanh((W_i h + b_i) / cap) and a log forget gate f = logsigmoid(cap tanh((W_f h + b_f) / cap)); with a running
+    maximum m (zero at a sequence's start) m' = max(f + m, i):
+
+        S' = exp(f + m - m') S + exp(i - m') k v^T,   n' likewise with k alone,
+        o  = S'^T q / (max(|n' . q|, exp(-m')) + 1e-6).
+
+    Each head's o is divided by its root mean square, the heads together are multiplied by a weight [heads x vdim]
+    and by sigmoid(W_g h), and projected by W_o. S and n are one state tensor [heads, vdim + 1, dim] (n is the column
+    of S that a value of 1 writes), m a second one [heads]; both float32, zero when a slot is taken, carried from
+    step to step. Gates, maximum, exponentials, state, read-out and norm are float32."""
+
+    def __init__(self, hidden_size: int, heads: int, dim: int, vdim: int, gate_cap: float, eps: float) -> None:
+        self.hidden_size, self.heads, self.dim, self.vdim = int(hidden_size), int(heads), int(dim), int(vdim)
+        self.gate_cap, self.eps = float(gate_cap), float(eps)
+        self.w_in = self.w_o = self.i_bias = self.f_bias = self.weight = None
+
+    @staticmethod
+    def parameters(hidden_size, heads, dim, vdim, **_) -> dict[str, ParamSpec]:
+        qk, values = int(heads) * int(dim), int(heads) * int(vdim)
+        return {"q": ParamSpec((qk, hidden_size)), "k": ParamSpec((qk, hidden_size)),
+                "v": ParamSpec((values, hidden_size)), "g": ParamSpec((values, hidden_size)),
+                "i": ParamSpec((int(heads), hidden_size)), "i_bias": ParamSpec((int(heads),)),
+                "f": ParamSpec((int(heads), hidden_size)), "f_bias": ParamSpec((int(heads),)),
+                "norm": ParamSpec((values,), "ones"), "o": ParamSpec((hidden_size, values))}
+
+    def supports(self, rt) -> str | None:
+        if self.dim % 4 or self.dim > 256:
+            return f"dim {self.dim}: the scan keeps a head's rows in 16-byte pieces, a multiple of 4 up to 256"
+        return row_rule(rt, hidden_size=self.hidden_size, **{"heads x vdim": self.heads * self.vdim})
+
+    def cache_need(self) -> CacheNeed:
+        return CacheNeed("several", parts=(CacheNeed("state", state_shape=(self.heads, self.vdim + 1, self.dim)),
+                                           CacheNeed("state", state_shape=(self.heads,))))
+
+    def bind(self, tensors, rt) -> None:
+        fused = torch.cat([tensors[name].to(rt.dtype) for name in ("q", "k", "v", "g", "i", "f")], dim=0)
+        self.w_in = fused.contiguous().to(rt.device)
+        self.w_o = rt.to_device(tensors["o"], rt.dtype)
+        self.i_bias = rt.to_device(tensors["i_bias"], torch.float32)
+        self.f_bias = rt.to_device(tensors["f_bias"], torch.float32)
+        self.weight = rt.to_device(tensors["norm"], torch.float32)
+
+    def forward(self, h: torch.Tensor, residual: torch.Tensor, batch, state, rt, write_cache: bool = True,
+                epilogue: int = ops.EPI_RESIDUAL) -> None:
+        n = batch.n_tokens
+        matrix, maximum = state
+        heads, qk, values = self.heads, self.heads * self.dim, self.heads * self.vdim
+        rows = rt.ws.buffer("mixer_rows", (n, 2 * qk + 2 * values + 2 * heads), torch.float32)
+        ops.gemm(rows, h, self.w_in, ops.EPI_STORE_F32)
+        aux = rt.ws.buffer("mixer_aux", (n, 3 * heads), torch.float32)
+        gates_at = 2 * qk + 2 * values
+        ops.running_max_gates(aux, rows, gates_at, gates_at + heads, self.i_bias, self.f_bias, self.gate_cap, heads,
+                              maximum, batch)
+        read = rt.ws.buffer("mixer_read", (n, values), torch.float32)
+        nq = rt.ws.buffer("mixer_nq", (n, heads), torch.float32)
+        ops.gated_scan(read, nq, rows, 0, qk, 2 * qk, heads, self.dim, self.vdim, aux, self.dim ** -0.5, matrix, batch)
+        gated = rt.ws.buffer("mixer_gated", (n, values), rt.dtype)
+        ops.normalised_readout(gated, read, nq, aux, 2 * heads, self.weight, rows, 2 * qk + values, heads, self.vdim,
+                               self.eps)
+        ops.gemm(residual, gated, self.w_o, epilogue)
+
+    def kernel_libraries(self, rt) -> set[str]:
+        return _libraries(rt)
+
+
 register_part("mixer", "decay_linear_attention", DecayLinearAttention)
+register_part("mixer", "gated_matrix_memory", GatedMatrixMemory)
 register_part("mixer", "gated_delta_rule", GatedDeltaRule)

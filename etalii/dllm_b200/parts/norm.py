@@ -46,16 +46,22 @@ class StreamOperand:
 
 
 class RMSNorm:
-    def __init__(self, hidden_size: int, eps: float) -> None:
-        self.hidden_size, self.eps = int(hidden_size), float(eps)
+    def __init__(self, hidden_size: int, eps: float, scalar: bool = False) -> None:
+        """`scalar`: the weight is ONE number for all coordinates (a tensor without dimensions in the checkpoint); on
+        the device it is spread over the row, so every kernel that applies a norm weight takes it."""
+        self.hidden_size, self.eps, self.scalar = int(hidden_size), float(eps), bool(scalar)
         self.weight = None
 
     @staticmethod
-    def parameters(hidden_size: int, eps: float) -> dict[str, ParamSpec]:
-        return {"weight": ParamSpec((int(hidden_size),), "ones")}
+    def parameters(hidden_size: int, eps: float, scalar: bool = False) -> dict[str, ParamSpec]:
+        return {"weight": ParamSpec(() if scalar else (int(hidden_size),), "ones")}
 
     def bind(self, tensors, rt) -> None:
-        self.weight = rt.to_device(tensors["weight"], torch.float32)
+        if self.scalar:
+            self.weight = tensors["weight"].to(torch.float32).reshape(1).expand(self.hidden_size).contiguous() \
+                .to(rt.device)
+        else:
+            self.weight = rt.to_device(tensors["weight"], torch.float32)
         self.folded = False
 
     def give_weight_to(self, consumer) -> bool:

@@ -1,10 +1,12 @@
 """Registries of part kinds. A part class is registered under a role ("norm", "position", "mixer", "feed_forward",
-"block", "embedding", "head", "reentry") and a kind name; `build_part` makes an instance from a `PartSpec`."""
+"block", "embedding", "head", "reentry", "filter", "token_input") and a kind name; `build_part` makes an instance from a `PartSpec`."""
 from __future__ import annotations
 
 from typing import Any, Callable
 
-ROLES = ("norm", "position", "mixer", "feed_forward", "block", "embedding", "head", "reentry")
+ROLES = ("norm", "position", "mixer", "feed_forward", "block", "embedding", "head", "reentry", "filter", "token_input")
+"""filter: something between a norm and the part that reads it, over time inside a sequence (a short causal
+convolution); token_input: something a layer adds to the stream from the step's token ids themselves."""
 _PARTS: dict[str, dict[str, Callable[..., Any]]] = {role: {} for role in ROLES}
 
 

@@ -56,11 +56,14 @@ class LayerSpec:
         """name -> role of this layer's parts, as its arrangement declares them; the names must match exactly."""
         from .registry import part_factory
 
-        wanted = dict(getattr(part_factory("block", self.block), "PARTS"))
-        if set(wanted) != set(self.parts):
-            raise ValueError(f"block {self.block!r} takes the parts {sorted(wanted)}; the layer gives "
-                             f"{sorted(self.parts)}")
-        return wanted
+        factory = part_factory("block", self.block)
+        wanted = dict(getattr(factory, "PARTS"))
+        optional = dict(getattr(factory, "OPTIONAL_PARTS", {}))  # (parts the arrangement runs without)
+        if not set(wanted) <= set(self.parts) <= set(wanted) | set(optional):
+            raise ValueError(f"block {self.block!r} takes the parts {sorted(wanted)}"
+                             + (f" and optionally {sorted(optional)}" if optional else "")
+                             + f"; the layer gives {sorted(self.parts)}")
+        return {name: (wanted.get(name) or optional[name]) for name in self.parts}
 
 
 @dataclass(frozen=True)
