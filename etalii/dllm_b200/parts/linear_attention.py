@@ -185,6 +185,9 @@ class GatedMatrixMemory:
     def __init__(self, hidden_size: int, heads: int, dim: int, vdim: int, gate_cap: float, eps: float) -> None:
         self.hidden_size, self.heads, self.dim, self.vdim = int(hidden_size), int(heads), int(dim), int(vdim)
         self.gate_cap, self.eps = float(gate_cap), float(eps)
+        self.padded = -(-self.dim // 4) * 4
+        """A head's q and k as the scan sees them: rows of zeros fill `dim` up to a multiple of 4 (they change no
+        q . k and leave their rows of S zero)."""
         self.w_in = self.w_o = self.i_bias = self.f_bias = self.weight = None
 
     @staticmethod
@@ -197,16 +200,24 @@ class GatedMatrixMemory:
                 "norm": ParamSpec((values,), "ones"), "o": ParamSpec((hidden_size, values))}
 
     def supports(self, rt) -> str | None:
-        if self.dim % 4 or self.dim > 256:
-            return f"dim {self.dim}: the scan keeps a head's rows in 16-byte pieces, a multiple of 4 up to 256"
+        if self.dim > 256:
+            return f"dim {self.dim}: the scan keeps a head's rows in registers, at most 256"
         return row_rule(rt, hidden_size=self.hidden_size, **{"heads x vdim": self.heads * self.vdim})
 
     def cache_need(self) -> CacheNeed:
-        return CacheNeed("several", parts=(CacheNeed("state", state_shape=(self.heads, self.vdim + 1, self.dim)),
+        return CacheNeed("several", parts=(CacheNeed("state", state_shape=(self.heads, self.vdim + 1, self.padded)),
                                            CacheNeed("state", state_shape=(self.heads,))))
 
     def bind(self, tensors, rt) -> None:
-        fused = torch.cat([tensors[name].to(rt.dtype) for name in ("q", "k", "v", "g", "i", "f")], dim=0)
+        def heads_padded(w):
+            if self.padded == self.dim:
+                return w.to(rt.dtype)
+            out = torch.zeros(self.heads, self.padded, self.hidden_size, dtype=rt.dtype)
+            out[:, :self.dim] = w.to(rt.dtype).view(self.heads, self.dim, self.hidden_size)
+            return out.view(self.heads * self.padded, self.hidden_size)
+
+        fused = torch.cat([heads_padded(tensors["q"]), heads_padded(tensors["k"])] +
+                          [tensors[name].to(rt.dtype) for name in ("v", "g", "i", "f")], dim=0)
         self.w_in = fused.contiguous().to(rt.device)
         self.w_o = rt.to_device(tensors["o"], rt.dtype)
         self.i_bias = rt.to_device(tensors["i_bias"], torch.float32)
@@ -217,7 +228,7 @@ class GatedMatrixMemory:
                 epilogue: int = ops.EPI_RESIDUAL) -> None:
         n = batch.n_tokens
         matrix, maximum = state
-        heads, qk, values = self.heads, self.heads * self.dim, self.heads * self.vdim
+        heads, qk, values = self.heads, self.heads * self.padded, self.heads * self.vdim
         rows = rt.ws.buffer("mixer_rows", (n, 2 * qk + 2 * values + 2 * heads), torch.float32)
         ops.gemm(rows, h, self.w_in, ops.EPI_STORE_F32)
         aux = rt.ws.buffer("mixer_aux", (n, 3 * heads), torch.float32)
@@ -226,7 +237,8 @@ class GatedMatrixMemory:
                               maximum, batch)
         read = rt.ws.buffer("mixer_read", (n, values), torch.float32)
         nq = rt.ws.buffer("mixer_nq", (n, heads), torch.float32)
-        ops.gated_scan(read, nq, rows, 0, qk, 2 * qk, heads, self.dim, self.vdim, aux, self.dim ** -0.5, matrix, batch)
+        ops.gated_scan(read, nq, rows, 0, qk, 2 * qk, heads, self.padded, self.vdim, aux, self.dim ** -0.5, matrix,
+                       batch)
         gated = rt.ws.buffer("mixer_gated", (n, values), rt.dtype)
         ops.normalised_readout(gated, read, nq, aux, 2 * heads, self.weight, rows, 2 * qk + values, heads, self.vdim,
                                self.eps)
