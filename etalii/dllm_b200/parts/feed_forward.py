@@ -131,6 +131,9 @@ class ActivationMLP:
         if ops.ACTIVATIONS.get(activation, 0) == 0:
             raise ValueError(f"activation {activation!r} is not known (gelu, gelu_tanh, relu_squared)")
         self.activation, self.biases, self.token_gate = activation, bool(biases), bool(token_gate)
+        if self.biases and self.token_gate:
+            raise ValueError("a token gate with biases is not built: the gate multiplies the activated values, and a "
+                             "bias behind the down product would escape it")
         self.padded = -(-self.intermediate_size // 8) * 8  # (the down product reads rows in 16-byte pieces)
         self.w_up = self.w_down = self.b_up = self.b_down = None
 

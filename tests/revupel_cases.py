@@ -58,9 +58,9 @@ CASES = {
     # one head, one tap, a memory head of six values (no 16-byte pieces), all experts chosen, a loop of one round from
     # the first layer on
     "narrow": lambda: config([
-        latent(heads=1, dim=8, rot_dim=2, vdim=12, q_rank=8, kv_rank=24, scale=0.5, base=50.0,
+        latent(heads=1, dim=8, rot_dim=2, vdim=16, q_rank=8, kv_rank=24, scale=0.5, base=50.0,
                mlp=moe(ff=8, experts=2, top=2, shared_ff=8)),
-        memory(heads=1, dim=6, vdim=20, gate_cap=3.0, mlp=None)], width=64, vocab=97, eps=3e-4, taps=1, side_dim=8,
+        memory(heads=1, dim=6, vdim=24, gate_cap=3.0, mlp=None)], width=64, vocab=97, eps=3e-4, taps=1, side_dim=8,
         loop=(0, 2, 1)),
 }
 
@@ -127,7 +127,7 @@ def random_weights(config_dict: dict, seed: int = 0) -> dict:
                 matrix(p + "mlp.router", mlp["router"]["experts"], width, 4.0)
                 for e in range(mlp["router"]["experts"]):
                     matrix(p + f"mlp.e{e}.up", mlp["expert"]["ff"], width, 1.5)
-                    matrix(p + f"mlp.e{e}.down", width, mlp["expert"]["ff"], 2.0)
+                    matrix(p + f"mlp.e{e}.down", width, mlp["expert"]["ff"], 1.0)
                 if mlp.get("shared") is not None:
                     matrix(p + "mlp.shared.up", mlp["shared"]["ff"], width, 1.5)
                     matrix(p + "mlp.shared.down", width, mlp["shared"]["ff"], 2.0)
