@@ -40,6 +40,7 @@ SOURCES = {
     "diff_attention_prefill": "diff_attention_prefill.cu",
     "diff_attention_decode": "diff_attention_decode.cu",
     "latent_attention": "latent_attention.cu",
+    "latent_attention_tiled": "latent_attention_tiled.cu",
     "moe": "moe.cu",
     "moe_grouped": "moe_grouped.cu",
     "sampling": "sampling.cu",

@@ -68,6 +68,9 @@ _prototypes = {
                                                   c_int, c_float, c_void_p, c_int, c_void_p],
     ("latent_attention", "dllm_latent_attention"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                                     c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
+    ("latent_attention_tiled", "dllm_latent_attention_tiled"): [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
+                                                                c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                                                c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
     ("latent_attention", "dllm_latent_values"): [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
                                                  c_int, c_int, c_void_p],
     ("recurrent", "dllm_gated_scan"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int,
@@ -647,10 +650,35 @@ def latent_values(out: torch.Tensor, mixed: torch.Tensor, uv: torch.Tensor, gate
         heads, rank, vdim, _code(out.dtype), _stream()), "latent_values")
 
 
-def latent_tiles(dtype, rank: int, rot: int):
-    """The tile shape of the tensor-core kernels for a latent of these sizes, or None where only the general kernel
-    runs (float32, or sizes the tiles do not take). No tensor-core kernel is built yet: always None."""
-    return None
+def latent_tiles(dtype, rank: int, rot: int, page_size: int = 64):
+    """The padded rank the tensor-core kernel runs a latent of these sizes with, or None where only the general kernel
+    runs: float32, a rank above 256, rows that are no whole 16-byte pieces, pages that are no multiple of 32."""
+    if dtype != torch.bfloat16 or rank > 256 or rank % 8 or (rank + rot) % 8 or rot % 2 or page_size % 32:
+        return None
+    return 64 if rank <= 64 else (128 if rank <= 128 else 256)
+
+
+def latent_attention_tiled(out: torch.Tensor, q: torch.Tensor, table: torch.Tensor | None, gates: torch.Tensor | None,
+                           gate_at: int, cache, heads: int, rank: int, rot: int, batch) -> None:
+    """`latent_attention` on the tensor cores over a bfloat16 cache. q float32 [tokens, heads x (rank + rot)] in the
+    latent's coordinates, scale included; with `table` its rotated parts are rotated on the way in. out [tokens,
+    heads x rank]: float32, or bfloat16; with `gates` (float32 rows, head h at column gate_at + h) every head's sum
+    is multiplied by the sigmoid of its gate."""
+    _cuda(out, q, table, gates)
+    assert q.dtype == torch.float32 and out.dtype in (torch.float32, torch.bfloat16)
+    assert cache.dtype == torch.bfloat16 and cache.keys_only and cache.kv_heads == 1 and cache.head_dim == rank + rot
+    assert q.shape[1] == heads * (rank + rot) and out.shape[1] == heads * rank and out.is_contiguous()
+    if table is not None:
+        assert table.dtype == torch.float32 and table.shape[0] > batch.max_position, "position beyond the table"
+        assert table.shape[1] == rot // 2 and table.shape[2] == 2
+    gate_ptr = (gates.data_ptr() + 4 * int(gate_at)) if gates is not None else None
+    _check(_fn("latent_attention_tiled", "dllm_latent_attention_tiled")(
+        q.data_ptr(), table.data_ptr() if table is not None else None, gate_ptr,
+        gates.shape[1] if gates is not None else 0, out.data_ptr(), 1 if out.dtype == torch.bfloat16 else 0,
+        cache.base_ptr, cache.page_table.data_ptr(), cache.max_pages, cache.page_size, heads, rank, rot,
+        batch.cu_seqlens.data_ptr(), batch.tok_pos.data_ptr(), batch.slots.data_ptr(), batch.n_seqs,
+        int(batch.max_new), _stream()), "latent_attention_tiled",
+        lambda: f"rank={rank} (a multiple of 8, at most 256) rot={rot} page={cache.page_size}")
 
 
 def running_max_gates(aux: torch.Tensor, rows: torch.Tensor, i_at: int, f_at: int, i_bias: torch.Tensor | None,

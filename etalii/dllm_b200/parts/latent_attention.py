@@ -11,7 +11,15 @@ Only [c | r] is cached, one row per position for all heads (a keys-only cache en
 heads' keys and values: since q_plain . W_uk c = (W_uk^T q_plain) . c, a query is taken into the latent's coordinates
 once and attention runs over the cached rows themselves, every head against the same rows; the weighted sum of c is
 then mapped through W_uv. Norms, rotation, scores, softmax and the gate are float32; the cache holds the activation
-type."""
+type.
+
+In bfloat16, with sizes the tile kernel takes, attention runs on the tensor cores (heads and tokens as rows of one
+query matrix over the shared rows). Steps of `MERGED_FROM` tokens or more also run with two merged weights made when the
+weights are bound: W_qa,h = scale [W_uk,h^T W_uq,h,plain ; W_uq,h,rot] takes the query latent straight into the
+latent's coordinates (one product for all heads, the rotation done as the attention kernel reads its queries), and
+W_ov = [W_o,h W_uv,h]_h takes the gated sums of c of all heads straight to the output (the gate is a number per token
+and head, so it can sit in front of both maps). That trades more multiply-adds (rank against dim and vdim) for plain
+tile products; single tokens keep the separate small maps, whose weights are fewer bytes to read."""
 from __future__ import annotations
 
 import torch
@@ -24,6 +32,9 @@ from .spec import ParamSpec
 
 
 class LatentAttention:
+    MERGED_FROM = 64
+    """Steps of this many tokens or more use the merged weights (bfloat16 tile path only)."""
+
     def __init__(self, hidden_size: int, num_heads: int, dim: int, rot_dim: int, vdim: int, q_rank: int, kv_rank: int,
                  scale: float, eps: float, position=None, gate: bool = True) -> None:
         self.hidden_size, self.num_heads = int(hidden_size), int(num_heads)
@@ -37,6 +48,7 @@ class LatentAttention:
             raise ValueError(f"the position encoding turns {self.position.rotary_dim} values, the rotated part has "
                              f"{self.rot_dim}")
         self.w_down = self.w_uq = self.w_uk = self.w_uv = self.w_o = self.q_weight = self.c_weight = None
+        self.w_qa = self.w_ov = None
 
     @staticmethod
     def parameters(hidden_size, num_heads, dim, rot_dim, vdim, q_rank, kv_rank, gate=True, **_) -> dict[str, ParamSpec]:
@@ -75,6 +87,17 @@ class LatentAttention:
         self.c_weight = rt.to_device(tensors["dkv_norm"], torch.float32)
         if self.position is not None:
             self.position.bind({}, rt)
+        if ops.latent_tiles(rt.dtype, self.kv_rank, self.rot_dim) is not None:
+            heads, dim, rot, vdim, rank = self.num_heads, self.dim, self.rot_dim, self.vdim, self.kv_rank
+            uq = tensors["uq"].to(device=rt.device, dtype=torch.float32).view(heads, dim + rot, self.q_rank)
+            uk = tensors["uk"].to(device=rt.device, dtype=torch.float32).view(heads, dim, rank)
+            uv = tensors["uv"].to(device=rt.device, dtype=torch.float32).view(heads, vdim, rank)
+            wo = tensors["o"].to(device=rt.device, dtype=torch.float32).view(self.hidden_size, heads, vdim)
+            absorbed = torch.bmm(uk.transpose(1, 2), uq[:, :dim])                     # [heads, rank, q_rank]
+            self.w_qa = (torch.cat([absorbed, uq[:, dim:]], dim=1) * self.scale).reshape(
+                heads * (rank + rot), self.q_rank).to(rt.dtype).contiguous()
+            self.w_ov = torch.einsum("whv,hvr->whr", wo, uv).reshape(self.hidden_size, heads * rank).to(
+                rt.dtype).contiguous()
 
     def forward(self, h: torch.Tensor, residual: torch.Tensor, batch, cache, rt, write_cache: bool = True,
                 epilogue: int = ops.EPI_RESIDUAL) -> None:
@@ -88,22 +111,24 @@ class LatentAttention:
         cq = rt.ws.buffer("latent_cq", (n, self.q_rank), rt.dtype)
         ops.latent_prepare(rows, 0, self.q_rank, self.q_rank, rank, rot, self.q_weight, self.c_weight, self.eps, table,
                            cq, cache, batch, write_cache)
+        gates, gate_at = (rows, self.q_rank + rank + rot) if self.gate else (None, 0)
+        tiles = ops.latent_tiles(rt.dtype, rank, rot, cache.page_size)
+        if tiles is not None and n >= self.MERGED_FROM and self.w_qa is not None:
+            q_lat = rt.ws.buffer("latent_q_abs", (n, heads * (rank + rot)), torch.float32)
+            ops.gemm(q_lat, cq, self.w_qa, ops.EPI_STORE_F32)
+            mixed = rt.ws.buffer("latent_mixed16", (n, heads * rank), rt.dtype)
+            ops.latent_attention_tiled(mixed, q_lat, table, gates, gate_at, cache, heads, rank, rot, batch)
+            ops.gemm(residual, mixed, self.w_ov, epilogue)
+            return
         q = rt.ws.buffer("latent_q", (n, heads * (dim + rot)), torch.float32)
         ops.gemm(q, cq, self.w_uq, ops.EPI_STORE_F32)
-        gates, gate_at = (rows, self.q_rank + rank + rot) if self.gate else (None, 0)
         attended = rt.ws.buffer("attended", (n, heads * vdim), rt.dtype)
-        tiles = ops.latent_tiles(rt.dtype, rank, rot)
+        q_lat = rt.ws.buffer("latent_q_abs", (n, heads * (rank + rot)), torch.float32)
+        ops.latent_queries(q_lat, q, self.w_uk, table, heads, dim, rot, rank, self.scale, batch)
+        mixed = rt.ws.buffer("latent_mixed", (n, heads * rank), torch.float32)
         if tiles is not None:
-            # bfloat16 on the tensor cores: queries absorbed and rounded, attention over the rows in tiles with the
-            # heads of a token as a tile's rows, the heads' values from the sums
-            q_lat = rt.ws.buffer("latent_q_abs16", (n, heads * (rank + rot)), torch.bfloat16)
-            ops.latent_queries_tiled(q_lat, q, self.w_uk, table, heads, dim, rot, rank, self.scale, batch)
-            mixed = rt.ws.buffer("latent_mixed", (n, heads * rank), torch.float32)
-            ops.latent_attention_tiled(mixed, q_lat, cache, heads, rank, rot, batch, rt.ws)
+            ops.latent_attention_tiled(mixed, q_lat, None, None, 0, cache, heads, rank, rot, batch)
         else:
-            q_lat = rt.ws.buffer("latent_q_abs", (n, heads * (rank + rot)), torch.float32)
-            ops.latent_queries(q_lat, q, self.w_uk, table, heads, dim, rot, rank, self.scale, batch)
-            mixed = rt.ws.buffer("latent_mixed", (n, heads * rank), torch.float32)
             ops.latent_attention(mixed, q_lat, cache, heads, rank, rot, batch)
         ops.latent_values(attended, mixed, self.w_uv, gates, gate_at, heads, rank, vdim)
         ops.gemm(residual, attended, self.w_o, epilogue)
