@@ -949,7 +949,72 @@ def satavik_rooflines(row: dict, size: dict, batch: int, peak: dict, contexts: l
     return out
 
 
-DESIGNS = {"tisalorn": ("Tisalorn", tisalorn_config), "satavik": ("Satavik", satavik_config)}
+def revupel_config(size: dict) -> dict:
+    """A Revupel model of `size`: latent attention and matrix memory in turn. The latent is twice a head wide (at most
+    256), the shared rotated key part half a head, the query latent three eighths of the width; the first layer's
+    feed-forward is dense, the others mix eight experts of a quarter of the feed-forward width, two a token, beside a
+    shared expert of half the width (the Satavik model's mixture); four taps; a second token embedding of 64 a layer."""
+    h, d, width = size["heads"], size["dim"], size["width"]
+    moe = {"kind": "moe", "expert": {"ff": size["ff"] // 4}, "router": {"experts": 8, "top": 2},
+           "shared": {"ff": size["ff"] // 2}}
+    latent = {"heads": h, "dim": d, "rot_dim": d // 2, "vdim": d, "q_rank": 3 * width // 8, "kv_rank": min(2 * d, 256),
+              "scale": (d + d // 2) ** -0.5, "rot": {"base": 500000.0, "dims": d // 2}}
+    memory = {"heads": h, "dim": d, "vdim": d, "gate_cap": 15.0}
+    layers = []
+    for i in range(size["layers"]):
+        mlp = {"kind": "dense", "ff": size["ff"]} if i == 0 else moe
+        layers.append({"type": "mlstm", "mixer": memory, "mlp": mlp} if i % 2 else
+                      {"type": "latent_attention", "mixer": latent, "mlp": mlp})
+    return {"architecture": "Revupel", "vocab": size["vocab"], "width": width, "norm": {"eps": 1e-6},
+            "canon": {"taps": 4}, "token_side": {"dim": 64}, "max_position": 8192, "layers": layers}
+
+
+def revupel_rooflines(row: dict, size: dict, batch: int, peak: dict, contexts: list) -> dict:
+    """The new kernels and the kernels of the models beside that do the like work, each against its own roofline.
+    Latent attention: a prompt step against its multiply-adds at the bf16 tensor rate (per query, key and head the
+    cache row as key and its first `rank` places as value; causal: half of tokens^2), a decode step against the cache
+    rows it must read at the HBM rate; beside the Satavik attention. The matrix memory: a decode step against the
+    matrices it reads and writes, a prompt step against its float32 multiply-adds; beside the Tisalorn decayed memory."""
+    h, d = size["heads"], size["dim"]
+    rank, rot = min(2 * d, 256), d // 2
+    out = {}
+
+    def put(name, work, kernel, unit):
+        if kernel and kernel["us"]:
+            rate = work / (kernel["us"] * 1e-6)
+            out[name] = round({"hbm": rate / 1e9 / peak["hbm_gbs"], "bf16": rate / 1e12 / peak["bf16_tflops"],
+                               "fp32": rate / (148 * 128 * 2 * 1.965e9)}[unit], 4)
+
+    put("revupel_attention_prefill_bf16_frac", 2 * h * (2 * rank + rot) * PREFILL_TOKENS * PREFILL_TOKENS / 2,
+        _first(row["revupel"]["prefill_kernels"], "latent_attention"), "bf16")
+    put("revupel_attention_decode_hbm_frac", 2 * sum(contexts) * (rank + rot),
+        _first(row["revupel"]["decode_kernels"], "latent_attention"), "hbm")
+    g = size["kv_heads"]
+    put("satavik_attention_prefill_bf16_frac", 2 * 2 * h * d * PREFILL_TOKENS * PREFILL_TOKENS / 2,
+        _first(row["satavik"]["prefill_kernels"], "diff_attention"), "bf16")
+    put("satavik_attention_decode_hbm_frac", 2 * sum(contexts) * g * 2 * d,
+        _first(row["satavik"]["decode_kernels"], "diff_attention"), "hbm")
+    for model, name, columns in (("revupel", "gated_scan", d + 1), ("tisalorn", "decay_scan", d)):
+        put(f"{model}_memory_decode_hbm_frac", 2 * 4 * batch * h * columns * d,
+            row[model]["decode_kernels"].get(name), "hbm")
+        put(f"{model}_memory_prefill_fp32_frac", 2 * 2 * PREFILL_TOKENS * h * columns * d,
+            row[model]["prefill_kernels"].get(name), "fp32")
+    # the experts run the Satavik model's kernels: a decode step against the weights touched (up and down here; gate,
+    # up and down there), a prompt step against the multiply-adds
+    touched, ff, width = min(8, 2 * batch), size["ff"], size["width"]
+    for model, products in (("revupel", 2), ("satavik", 3)):
+        for phase, work, unit in (("decode", 2 * touched * products * (ff // 4) * width, "hbm"),
+                                  ("prefill", 2 * PREFILL_TOKENS * 2 * products * (ff // 4) * width, "bf16")):
+            kernels = row[model][phase + "_kernels"]
+            us = sum(k["us"] * k["launches"] for name, k in kernels.items() if name.startswith("moe_")) / \
+                max(1, (_first(kernels, "moe_route") or {"launches": 1})["launches"])
+            put(f"{model}_experts_{phase}_{unit}_frac", work, {"us": us}, unit)
+    return out
+
+
+DESIGNS = {"tisalorn": ("Tisalorn", tisalorn_config, ("llama",)), "satavik": ("Satavik", satavik_config, ("llama",)),
+           "revupel": ("Revupel", revupel_config, ("satavik", "tisalorn"))}
+"""--design NAME: the design's name, its configuration at a size, and the models it is measured beside."""
 
 
 def design_comparison(args) -> int:
@@ -968,7 +1033,10 @@ def design_comparison(args) -> int:
 
     peak = peaks()
     design = args.design
-    out = {"design": DESIGNS[design][0], "beside": "llama of equal width, heads, feed-forward and depth", "dtype": "bf16",
+    beside = DESIGNS[design][2]
+    configs = {"llama": llama_config_of, **{name: entry[1] for name, entry in DESIGNS.items()}}
+    out = {"design": DESIGNS[design][0], "beside": " and ".join(beside) + " of equal width, heads, feed-forward and depth",
+           "dtype": "bf16",
            "data": "synthetic: seeded random token ids, seeded random weights", "batch": args.batch,
            "prefill_tokens": PREFILL_TOKENS, "peaks": peak["source"], "sizes": {}}
     warmup = max(3, args.warmup)
@@ -976,7 +1044,7 @@ def design_comparison(args) -> int:
     for size_name in (args.size.split(",") if args.size else sorted(DESIGN_SIZES)):
         size = DESIGN_SIZES[size_name]
         row = {"config": size}
-        for model, config_dict in ((design, DESIGNS[design][1](size)), ("llama", llama_config_of(size))):
+        for model, config_dict in ((name, configs[name](size)) for name in (design, *beside)):
             config = config_from_dict(config_dict)
             cache_tokens = 64 * (-(-(PREFILL_TOKENS + warmup + steps + 64) // 64)) * max(args.batch, 2)
             engine = Engine.from_random(config, seed=0, dtype="bfloat16", device="cuda:0", max_tokens=cache_tokens,
@@ -1028,11 +1096,14 @@ def design_comparison(args) -> int:
         # the new kernels against their rooflines
         if design == "tisalorn":
             row["roofline"] = tisalorn_rooflines(row, size, args.batch, peak)
-        else:
+        elif design == "satavik":
             row["roofline"] = satavik_rooflines(row, size, args.batch, peak, [len(p) + 1 for p in prompts])
-        row[design + "_over_llama"] = {
-            "prefill": round(row[design]["prefill_tokens_per_s"] / row["llama"]["prefill_tokens_per_s"], 3),
-            "decode": round(row[design]["decode_tokens_per_s"] / row["llama"]["decode_tokens_per_s"], 3)}
+        else:
+            row["roofline"] = revupel_rooflines(row, size, args.batch, peak, [len(p) + 1 for p in prompts])
+        for other in beside:
+            row[f"{design}_over_{other}"] = {
+                "prefill": round(row[design]["prefill_tokens_per_s"] / row[other]["prefill_tokens_per_s"], 3),
+                "decode": round(row[design]["decode_tokens_per_s"] / row[other]["decode_tokens_per_s"], 3)}
         out["sizes"][size_name] = row
     if args.profile not in ("prefill", "decode"):
         print(json.dumps(out))
@@ -1043,7 +1114,7 @@ def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--design", choices=sorted(DESIGNS),
                         help="instead of the benchmark: prefill and decode throughput of this design at layer sizes "
-                             "like a real model's, beside a Llama model of equal size, and its kernels' rooflines")
+                             "like a real model's, beside the closest models of equal size, and its kernels' rooflines")
     parser.add_argument("--size", default="", help="with --design: which sizes (comma separated; default all)")
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=256)

@@ -12,6 +12,10 @@
 // the weighted sum of c per pair: float32, or multiplied by the pair's gate sigmoid(z) and rounded to bfloat16 (the
 // operand of a product over all heads' sums).
 //
+// Few rows over a long context (single tokens) would leave most multiprocessors idle: with `splits` > 1 the key tiles of
+// a sequence are dealt to that many blocks, each leaves its rows' unnormalised sums with their maximum and total in
+// scratch, and `latent_combine` merges them (and applies gate and rounding).
+//
 // rank: a multiple of 8, at most 256 (a warp keeps 16 x rank sums in registers; instantiated for 64, 128, 256).
 // rank + rot: a multiple of 8 (cache rows are copied in 16-byte pieces). page_size: a multiple of 32.
 #include "common.cuh"
@@ -62,6 +66,9 @@ struct TiledArgs {
   const int* tok_pos;
   const int* slots;
   int heads, rank, rot, ld;  // ld: elements of a shared-memory row
+  int splits;                // blocks that share a sequence's keys (blockIdx.z)
+  float* part_o;             // splits > 1: [pair][split][rank] unnormalised sums
+  float* part_ml;            // splits > 1: [pair][split][2] maximum (in units of log2 e) and total
 };
 
 template <int RANK>
@@ -97,8 +104,21 @@ __global__ void __launch_bounds__(THREADS) latent_tiled_kernel(TiledArgs a) {
     }
   };
   const int last_pos = first_pos + (int)((p0 + rows - 1) / heads);
-  const int kt_end = last_pos / BN;
-  load_keys(0, 0);
+  int kt_begin = 0, kt_end = last_pos / BN;
+  if (a.splits > 1) {
+    int per = (kt_end + a.splits) / a.splits;  // ceil((kt_end + 1) / splits)
+    kt_begin = blockIdx.z * per;
+    kt_end = min(kt_end, kt_begin + per - 1);
+    if (kt_begin > kt_end) {  // nothing left for this block: its rows count for nothing
+      for (int i = tid; i < rows; i += THREADS) {
+        float* ml = a.part_ml + (((size_t)tok0 * heads + p0 + i) * a.splits + blockIdx.z) * 2;
+        ml[0] = -INFINITY;
+        ml[1] = 0.f;
+      }
+      return;
+    }
+  }
+  load_keys(0, kt_begin);
   cp_async_commit();
 
   // the queries, rotated where that is still to do, as bfloat16
@@ -137,8 +157,8 @@ __global__ void __launch_bounds__(THREADS) latent_tiled_kernel(TiledArgs a) {
   const int warp_last_pos = warp_rows > 0 ? first_pos + (int)((p0 + warp * 16 + warp_rows - 1) / heads) : -1;
   const int k_steps = (width + 15) >> 4;
 
-  for (int kt = 0; kt <= kt_end; ++kt) {
-    const int stage = kt & 1;
+  for (int kt = kt_begin; kt <= kt_end; ++kt) {
+    const int stage = (kt - kt_begin) & 1;
     if (kt + 1 <= kt_end) load_keys(stage ^ 1, kt + 1);
     cp_async_commit();
     cp_async_wait<1>();
@@ -225,6 +245,25 @@ __global__ void __launch_bounds__(THREADS) latent_tiled_kernel(TiledArgs a) {
     l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);
     l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 2);
   }
+  if (a.splits > 1) {
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      int r = warp * 16 + gq + half * 8;
+      if (r >= rows) continue;
+      size_t at = ((size_t)tok0 * heads + p0 + r) * a.splits + blockIdx.z;
+      if (tq == 0) {
+        a.part_ml[at * 2] = m_run[half];
+        a.part_ml[at * 2 + 1] = l_run[half];
+      }
+#pragma unroll
+      for (int i = 0; i < RANK / 8; ++i) {
+        int d = i * 8 + tq * 2;
+        if (d < a.rank)
+          *reinterpret_cast<float2*>(a.part_o + at * a.rank + d) = make_float2(o_acc[i][half * 2], o_acc[i][half * 2 + 1]);
+      }
+    }
+    return;
+  }
 #pragma unroll
   for (int half = 0; half < 2; ++half) {
     int r = warp * 16 + gq + half * 8;
@@ -247,6 +286,34 @@ __global__ void __launch_bounds__(THREADS) latent_tiled_kernel(TiledArgs a) {
   }
 }
 
+// A block per (token, head) pair: the splits' sums weighted by 2^(their maximum - the largest), divided by the total.
+__global__ void __launch_bounds__(128) latent_combine_kernel(TiledArgs a, long long pairs) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long p = blockIdx.x;
+  if (p >= pairs) return;
+  const float* ml = a.part_ml + (size_t)p * a.splits * 2;
+  float top = -INFINITY;
+  for (int z = 0; z < a.splits; ++z) top = fmaxf(top, ml[2 * z]);
+  float total = 0.f;
+  for (int z = 0; z < a.splits; ++z)
+    if (ml[2 * z] != -INFINITY) total += fast_exp2(ml[2 * z] - top) * ml[2 * z + 1];
+  float factor = 1.0f / total;
+  if (a.gates != nullptr) {
+    float z = a.gates[(size_t)(p / a.heads) * a.gate_ld + (int)(p % a.heads)];
+    factor *= z >= 0.f ? 1.0f / (1.0f + expf(-z)) : expf(z) / (1.0f + expf(z));
+  }
+  const float* o = a.part_o + (size_t)p * a.splits * a.rank;
+  for (int d = threadIdx.x; d < a.rank; d += blockDim.x) {
+    float sum = 0.f;
+    for (int z = 0; z < a.splits; ++z)
+      if (ml[2 * z] != -INFINITY) sum = fmaf(fast_exp2(ml[2 * z] - top), o[(size_t)z * a.rank + d], sum);
+    sum *= factor;
+    if (a.out_bf16) ((bf16*)a.out)[(size_t)p * a.rank + d] = __float2bfloat16_rn(sum);
+    else ((float*)a.out)[(size_t)p * a.rank + d] = sum;
+  }
+}
+
 template <int RANK>
 int launch(const TiledArgs& a, int tiles, int n_seqs, cudaStream_t stream) {
   size_t smem = (size_t)(BM + 2 * BN) * a.ld * sizeof(bf16);
@@ -257,17 +324,19 @@ int launch(const TiledArgs& a, int tiles, int n_seqs, cudaStream_t stream) {
       return DLLM_LAUNCH_FAILED;
     configured = smem;
   }
-  return dllm_launch_pdl(latent_tiled_kernel<RANK>, dim3(tiles, n_seqs), dim3(THREADS), smem, stream, a);
+  return dllm_launch_pdl(latent_tiled_kernel<RANK>, dim3(tiles, n_seqs, a.splits), dim3(THREADS), smem, stream, a);
 }
 }  // namespace
 
 // max_new: the most new tokens any sequence of the step has (the grid covers that many pairs for every sequence;
-// blocks beyond a sequence's own pairs leave at once).
+// blocks beyond a sequence's own pairs leave at once). splits > 1: part_o [pairs, splits, rank] and part_ml [pairs,
+// splits, 2] float32 scratch, pairs = the step's tokens x heads.
 DLLM_EXPORT int dllm_latent_attention_tiled(const float* q, const float* table, const float* gates, int gate_ld,
                                             void* out, int out_bf16, const void* cache, const int* page_table,
                                             int max_pages, int page_size, int heads, int rank, int rot,
                                             const int* cu_seqlens, const int* tok_pos, const int* slots, int n_seqs,
-                                            int max_new, cudaStream_t stream) {
+                                            int max_new, int splits, float* part_o, float* part_ml, long long pairs,
+                                            cudaStream_t stream) {
   if (n_seqs <= 0 || max_new <= 0) return DLLM_OK;
   if (heads <= 0 || rank <= 0 || rank > 256 || (rank & 7) || rot < 0 || (rot & 1) || ((rank + rot) & 7) ||
       page_size <= 0 || page_size % BN || n_seqs > 65535)
@@ -278,10 +347,12 @@ DLLM_EXPORT int dllm_latent_attention_tiled(const float* q, const float* table, 
   int ld = (k_width > padded_rank ? k_width : padded_rank) + 8;
   if ((size_t)(BM + 2 * BN) * ld * sizeof(bf16) > 200 * 1024) return DLLM_UNSUPPORTED_SIZE;
   TiledArgs a{q, rot > 0 ? table : nullptr, gates, gate_ld, out, out_bf16, (const bf16*)cache, page_table, max_pages,
-              page_size, cu_seqlens, tok_pos, slots, heads, rank, rot, ld};
-  long long pairs = (long long)max_new * heads;
-  int tiles = (int)((pairs + BM - 1) / BM);
-  if (rank <= 64) return launch<64>(a, tiles, n_seqs, stream);
-  if (rank <= 128) return launch<128>(a, tiles, n_seqs, stream);
-  return launch<256>(a, tiles, n_seqs, stream);
+              page_size, cu_seqlens, tok_pos, slots, heads, rank, rot, ld, splits, part_o, part_ml};
+  if (splits < 1 || splits > 64 || (splits > 1 && (!part_o || !part_ml || pairs <= 0))) return DLLM_BAD_ARGUMENT;
+  long long most = (long long)max_new * heads;
+  int tiles = (int)((most + BM - 1) / BM);
+  int status = rank <= 64 ? launch<64>(a, tiles, n_seqs, stream)
+                          : (rank <= 128 ? launch<128>(a, tiles, n_seqs, stream) : launch<256>(a, tiles, n_seqs, stream));
+  if (status != DLLM_OK || splits == 1) return status;
+  return dllm_launch_pdl(latent_combine_kernel, dim3((unsigned)pairs), dim3(128), 0, stream, a, pairs);
 }

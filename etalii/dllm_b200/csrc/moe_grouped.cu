@@ -16,7 +16,7 @@ namespace {
 typedef __nv_bfloat16 bf16;
 constexpr int BM = 128, BN = 128, BK = 64, STAGES = 3, THREADS = 256, LDS = BK + 8;
 constexpr int MAX_EXPERTS = 256;
-constexpr int EPI_GLU = 0, EPI_SCATTER = 1;
+constexpr int EPI_GLU = 0, EPI_SCATTER = 1, EPI_ACT = 2;
 
 __device__ __forceinline__ void cp_async_16(void* smem, const void* gmem, bool valid) {
   unsigned s = (unsigned)__cvta_generic_to_shared(smem);
@@ -72,10 +72,18 @@ struct GroupedArgs {
   const bf16* w;          // [experts, n, k]
   int n, k, experts;
   const int* offsets;
-  bf16* act;              // EPI_GLU: [places, n / 2]
+  bf16* act;              // EPI_GLU: [places, n / 2]; EPI_ACT: [places, n]
   float* y;               // EPI_SCATTER: [pairs, n]
   float limit, alpha, shift;
+  int kind;               // EPI_ACT: 1 gelu (erf), 2 gelu (tanh form), 3 the square of relu
 };
+
+__device__ __forceinline__ float plain_activation(float z, int kind) {
+  if (kind == 1) return 0.5f * z * (1.0f + erff(z * 0.70710678118654752440f));
+  if (kind == 2) return 0.5f * z * (1.0f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
+  float r = fmaxf(z, 0.f);
+  return r * r;
+}
 
 template <int EPI>
 __global__ void __launch_bounds__(THREADS) grouped_kernel(GroupedArgs g) {
@@ -183,6 +191,15 @@ __global__ void __launch_bounds__(THREADS) grouped_kernel(GroupedArgs g) {
             dst[n / 2] = __float2bfloat16_rn(gate / (1.0f + expf(-g.alpha * gate)) * (up + g.shift));
           }
         }
+      } else if (EPI == EPI_ACT) {
+        bf16* dst = g.act + (size_t)place * g.n;
+#pragma unroll
+        for (int nj = 0; nj < 4; ++nj) {
+          int n = n0 + warp_n * 32 + nj * 8 + tq * 2;
+          float lo = plain_activation(acc[mi][nj][half * 2], g.kind), hi = plain_activation(acc[mi][nj][half * 2 + 1], g.kind);
+          if (n + 1 < g.n) *reinterpret_cast<__nv_bfloat162*>(dst + n) = __floats2bfloat162_rn(lo, hi);
+          else if (n < g.n) dst[n] = __float2bfloat16_rn(lo);
+        }
       } else {
         float* dst = g.y + (size_t)g.place_pair[place] * g.n;
 #pragma unroll
@@ -240,8 +257,22 @@ DLLM_EXPORT int dllm_moe_grouped_up(void* act, const void* h, int width, const v
   if (width <= 0 || (width & 7) || ff <= 0 || experts <= 0 || experts > MAX_EXPERTS || top <= 0)
     return DLLM_UNSUPPORTED_SIZE;
   GroupedArgs g{(const bf16*)h, width, place_pair, 1, top, (const bf16*)w_gate_up, 2 * ff, width, experts, offsets,
-                (bf16*)act, nullptr, limit, alpha, shift};
+                (bf16*)act, nullptr, limit, alpha, shift, 0};
   return launch_grouped<EPI_GLU>(g, tokens * top, stream);
+}
+
+// act [pairs, ff] bfloat16 in expert order = activation(W_up[expert] h[token]) for experts without a gate matrix;
+// w_up [experts, ff, width]; ff even (a pair of values a store).
+DLLM_EXPORT int dllm_moe_grouped_up_plain(void* act, const void* h, int width, const void* w_up, int ff, int experts,
+                                          int top, int tokens, const int* offsets, const int* place_pair, int kind,
+                                          cudaStream_t stream) {
+  if (tokens <= 0) return DLLM_OK;
+  if (width <= 0 || (width & 7) || ff <= 0 || (ff & 1) || experts <= 0 || experts > MAX_EXPERTS || top <= 0)
+    return DLLM_UNSUPPORTED_SIZE;
+  if (kind < 1 || kind > 3) return DLLM_BAD_ARGUMENT;
+  GroupedArgs g{(const bf16*)h, width, place_pair, 1, top, (const bf16*)w_up, ff, width, experts, offsets, (bf16*)act,
+                nullptr, 0.f, 0.f, 0.f, kind};
+  return launch_grouped<EPI_ACT>(g, tokens * top, stream);
 }
 
 // y [pairs, width] float32 by pair = W_down[expert] act[place]; act [pairs, ff] bfloat16 in expert order.
@@ -252,7 +283,7 @@ DLLM_EXPORT int dllm_moe_grouped_down(float* y, const void* act, int ff, const v
   if (width <= 0 || (width & 1) || ff <= 0 || (ff & 7) || experts <= 0 || experts > MAX_EXPERTS || top <= 0)
     return DLLM_UNSUPPORTED_SIZE;
   GroupedArgs g{(const bf16*)act, ff, place_pair, 0, top, (const bf16*)w_down, width, ff, experts, offsets, nullptr, y,
-                0.f, 0.f, 0.f};
+                0.f, 0.f, 0.f, 0};
   return launch_grouped<EPI_SCATTER>(g, tokens * top, stream);
 }
 

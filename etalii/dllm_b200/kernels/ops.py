@@ -70,7 +70,8 @@ _prototypes = {
                                                     c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
     ("latent_attention_tiled", "dllm_latent_attention_tiled"): [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
                                                                 c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                                                                c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
+                                                                c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                                                c_void_p, c_void_p, ctypes.c_longlong, c_void_p],
     ("latent_attention", "dllm_latent_values"): [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
                                                  c_int, c_int, c_void_p],
     ("recurrent", "dllm_gated_scan"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int,
@@ -87,6 +88,8 @@ _prototypes = {
     ("moe_grouped", "dllm_moe_sort"): [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p],
     ("moe_grouped", "dllm_moe_grouped_up"): [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
                                              c_void_p, c_float, c_float, c_float, c_void_p],
+    ("moe_grouped", "dllm_moe_grouped_up_plain"): [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
+                                                   c_void_p, c_void_p, c_int, c_void_p],
     ("moe_grouped", "dllm_moe_grouped_down"): [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
                                                c_void_p, c_void_p, c_void_p],
     ("moe_grouped", "dllm_moe_combine"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
@@ -514,8 +517,8 @@ def moe_up_plain(act: torch.Tensor, h: torch.Tensor, w_up: torch.Tensor, chosen:
 
 
 def moe_plain_grouped_built() -> bool:
-    """Whether the grouped tile products know experts without a gate matrix (not yet: the per-token kernels run)."""
-    return False
+    """Whether the grouped tile products know experts without a gate matrix."""
+    return True
 
 
 def norm_conv(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, taps: torch.Tensor,
@@ -658,8 +661,15 @@ def latent_tiles(dtype, rank: int, rot: int, page_size: int = 64):
     return 64 if rank <= 64 else (128 if rank <= 128 else 256)
 
 
+def latent_splits(batch, heads: int) -> int:
+    """Over how many blocks the tile kernel deals a sequence's keys: one where the step's rows fill the
+    multiprocessors by themselves, else enough for two blocks each, every block with 128 positions or more."""
+    blocks = batch.n_seqs * (-(-batch.max_new * heads // 64))
+    return max(1, min(64, 296 // max(1, blocks), batch.max_context // 128))
+
+
 def latent_attention_tiled(out: torch.Tensor, q: torch.Tensor, table: torch.Tensor | None, gates: torch.Tensor | None,
-                           gate_at: int, cache, heads: int, rank: int, rot: int, batch) -> None:
+                           gate_at: int, cache, heads: int, rank: int, rot: int, batch, ws=None) -> None:
     """`latent_attention` on the tensor cores over a bfloat16 cache. q float32 [tokens, heads x (rank + rot)] in the
     latent's coordinates, scale included; with `table` its rotated parts are rotated on the way in. out [tokens,
     heads x rank]: float32, or bfloat16; with `gates` (float32 rows, head h at column gate_at + h) every head's sum
@@ -672,12 +682,17 @@ def latent_attention_tiled(out: torch.Tensor, q: torch.Tensor, table: torch.Tens
         assert table.dtype == torch.float32 and table.shape[0] > batch.max_position, "position beyond the table"
         assert table.shape[1] == rot // 2 and table.shape[2] == 2
     gate_ptr = (gates.data_ptr() + 4 * int(gate_at)) if gates is not None else None
+    pairs = batch.n_tokens * heads
+    splits = latent_splits(batch, heads) if ws is not None else 1
+    part_o = ws.buffer("latent_part_o", (pairs * splits * rank,), torch.float32) if splits > 1 else None
+    part_ml = ws.buffer("latent_part_ml", (pairs * splits * 2,), torch.float32) if splits > 1 else None
     _check(_fn("latent_attention_tiled", "dllm_latent_attention_tiled")(
         q.data_ptr(), table.data_ptr() if table is not None else None, gate_ptr,
         gates.shape[1] if gates is not None else 0, out.data_ptr(), 1 if out.dtype == torch.bfloat16 else 0,
         cache.base_ptr, cache.page_table.data_ptr(), cache.max_pages, cache.page_size, heads, rank, rot,
         batch.cu_seqlens.data_ptr(), batch.tok_pos.data_ptr(), batch.slots.data_ptr(), batch.n_seqs,
-        int(batch.max_new), _stream()), "latent_attention_tiled",
+        int(batch.max_new), splits, part_o.data_ptr() if splits > 1 else None,
+        part_ml.data_ptr() if splits > 1 else None, pairs, _stream()), "latent_attention_tiled",
         lambda: f"rank={rank} (a multiple of 8, at most 256) rot={rot} page={cache.page_size}")
 
 
@@ -777,6 +792,37 @@ def moe_experts_grouped(out: torch.Tensor, h: torch.Tensor, w_gate_up: torch.Ten
         act.data_ptr(), h.data_ptr(), width, w_gate_up.data_ptr(), ff, experts, int(top), tokens, offsets.data_ptr(),
         place_pair.data_ptr(), float(limit), float(alpha), float(shift), stream), "moe_grouped_up",
         lambda: f"width={width} (a multiple of 8)")
+    _check(_fn("moe_grouped", "dllm_moe_grouped_down")(
+        y.data_ptr(), act.data_ptr(), ff, w_down.data_ptr(), width, experts, int(top), tokens, offsets.data_ptr(),
+        place_pair.data_ptr(), stream), "moe_grouped_down", lambda: f"ff={ff} (a multiple of 8)")
+    _check(_fn("moe_grouped", "dllm_moe_combine")(out.data_ptr(), y.data_ptr(), weights.data_ptr(), width, int(top),
+                                                  tokens, 1 if accumulate else 0, stream), "moe_combine")
+
+
+def moe_plain_experts_grouped(out: torch.Tensor, h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor,
+                              chosen: torch.Tensor, weights: torch.Tensor, top: int, kind: int, offsets: torch.Tensor,
+                              place_pair: torch.Tensor, act: torch.Tensor, y: torch.Tensor,
+                              accumulate: bool = False) -> None:
+    """`moe_experts_grouped` for experts without a gate matrix: W_down act(W_up h) with the activation `kind` in the
+    first product's epilogue. w_up [experts, ff, width], w_down [experts, width, ff]; the same scratch."""
+    _cuda(out, h, w_up, w_down, chosen, weights, offsets, place_pair, act, y)
+    tokens, width = h.shape
+    experts, ff = w_up.shape[0], w_up.shape[1]
+    pairs = tokens * top
+    assert h.dtype == torch.bfloat16 and w_up.dtype == torch.bfloat16 and w_down.dtype == torch.bfloat16
+    assert tuple(w_down.shape) == (experts, width, ff) and w_up.shape[2] == width
+    assert out.dtype == torch.float32 and tuple(out.shape) == (tokens, width)
+    assert offsets.dtype == torch.int32 and offsets.numel() >= experts + 1 and place_pair.numel() >= pairs
+    assert act.dtype == torch.bfloat16 and act.numel() >= pairs * ff and y.dtype == torch.float32
+    assert y.numel() >= pairs * width and chosen.dtype == torch.int32 and weights.dtype == torch.float32
+    stream = _stream()
+    _check(_fn("moe_grouped", "dllm_moe_sort")(chosen.data_ptr(), pairs, experts, offsets.data_ptr(),
+                                               place_pair.data_ptr(), stream), "moe_sort",
+           lambda: f"experts={experts} (at most 256)")
+    _check(_fn("moe_grouped", "dllm_moe_grouped_up_plain")(
+        act.data_ptr(), h.data_ptr(), width, w_up.data_ptr(), ff, experts, int(top), tokens, offsets.data_ptr(),
+        place_pair.data_ptr(), int(kind), stream), "moe_grouped_up",
+        lambda: f"width={width} (a multiple of 8) ff={ff} (even)")
     _check(_fn("moe_grouped", "dllm_moe_grouped_down")(
         y.data_ptr(), act.data_ptr(), ff, w_down.data_ptr(), width, experts, int(top), tokens, offsets.data_ptr(),
         place_pair.data_ptr(), stream), "moe_grouped_down", lambda: f"ff={ff} (a multiple of 8)")

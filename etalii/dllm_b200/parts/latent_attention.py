@@ -14,12 +14,12 @@ then mapped through W_uv. Norms, rotation, scores, softmax and the gate are floa
 type.
 
 In bfloat16, with sizes the tile kernel takes, attention runs on the tensor cores (heads and tokens as rows of one
-query matrix over the shared rows). Steps of `MERGED_FROM` tokens or more also run with two merged weights made when the
-weights are bound: W_qa,h = scale [W_uk,h^T W_uq,h,plain ; W_uq,h,rot] takes the query latent straight into the
-latent's coordinates (one product for all heads, the rotation done as the attention kernel reads its queries), and
-W_ov = [W_o,h W_uv,h]_h takes the gated sums of c of all heads straight to the output (the gate is a number per token
-and head, so it can sit in front of both maps). That trades more multiply-adds (rank against dim and vdim) for plain
-tile products; single tokens keep the separate small maps, whose weights are fewer bytes to read."""
+query matrix over the shared rows) with two merged weights made when the weights are bound:
+W_qa,h = scale [W_uk,h^T W_uq,h,plain ; W_uq,h,rot] takes the query latent straight into the latent's coordinates (one
+product for all heads, the rotation done as the attention kernel reads its queries), and W_ov = [W_o,h W_uv,h]_h takes
+the gated sums of c of all heads straight to the output (the gate is a number per token and head, so it can sit in
+front of both maps). That trades more multiply-adds and weight bytes (rank against dim and vdim) for two plain
+products in place of four and two small per-head kernels; the separate maps are then not kept on the device."""
 from __future__ import annotations
 
 import torch
@@ -32,9 +32,6 @@ from .spec import ParamSpec
 
 
 class LatentAttention:
-    MERGED_FROM = 64
-    """Steps of this many tokens or more use the merged weights (bfloat16 tile path only)."""
-
     def __init__(self, hidden_size: int, num_heads: int, dim: int, rot_dim: int, vdim: int, q_rank: int, kv_rank: int,
                  scale: float, eps: float, position=None, gate: bool = True) -> None:
         self.hidden_size, self.num_heads = int(hidden_size), int(num_heads)
@@ -79,10 +76,6 @@ class LatentAttention:
         names = ("dq", "dkv", "g") if self.gate else ("dq", "dkv")
         fused = torch.cat([tensors[name].to(rt.dtype) for name in names], dim=0)
         self.w_down = fused.contiguous().to(rt.device)
-        self.w_uq = rt.to_device(tensors["uq"], rt.dtype)
-        self.w_uk = rt.to_device(tensors["uk"], rt.dtype)
-        self.w_uv = rt.to_device(tensors["uv"], rt.dtype)
-        self.w_o = rt.to_device(tensors["o"], rt.dtype)
         self.q_weight = rt.to_device(tensors["dq_norm"], torch.float32)
         self.c_weight = rt.to_device(tensors["dkv_norm"], torch.float32)
         if self.position is not None:
@@ -98,6 +91,11 @@ class LatentAttention:
                 heads * (rank + rot), self.q_rank).to(rt.dtype).contiguous()
             self.w_ov = torch.einsum("whv,hvr->whr", wo, uv).reshape(self.hidden_size, heads * rank).to(
                 rt.dtype).contiguous()
+            return
+        self.w_uq = rt.to_device(tensors["uq"], rt.dtype)
+        self.w_uk = rt.to_device(tensors["uk"], rt.dtype)
+        self.w_uv = rt.to_device(tensors["uv"], rt.dtype)
+        self.w_o = rt.to_device(tensors["o"], rt.dtype)
 
     def forward(self, h: torch.Tensor, residual: torch.Tensor, batch, cache, rt, write_cache: bool = True,
                 epilogue: int = ops.EPI_RESIDUAL) -> None:
@@ -112,12 +110,13 @@ class LatentAttention:
         ops.latent_prepare(rows, 0, self.q_rank, self.q_rank, rank, rot, self.q_weight, self.c_weight, self.eps, table,
                            cq, cache, batch, write_cache)
         gates, gate_at = (rows, self.q_rank + rank + rot) if self.gate else (None, 0)
-        tiles = ops.latent_tiles(rt.dtype, rank, rot, cache.page_size)
-        if tiles is not None and n >= self.MERGED_FROM and self.w_qa is not None:
+        if self.w_qa is not None:
+            if ops.latent_tiles(rt.dtype, rank, rot, cache.page_size) is None:
+                raise ValueError(f"pages of {cache.page_size} positions: the tile kernel takes multiples of 32")
             q_lat = rt.ws.buffer("latent_q_abs", (n, heads * (rank + rot)), torch.float32)
             ops.gemm(q_lat, cq, self.w_qa, ops.EPI_STORE_F32)
             mixed = rt.ws.buffer("latent_mixed16", (n, heads * rank), rt.dtype)
-            ops.latent_attention_tiled(mixed, q_lat, table, gates, gate_at, cache, heads, rank, rot, batch)
+            ops.latent_attention_tiled(mixed, q_lat, table, gates, gate_at, cache, heads, rank, rot, batch, rt.ws)
             ops.gemm(residual, mixed, self.w_ov, epilogue)
             return
         q = rt.ws.buffer("latent_q", (n, heads * (dim + rot)), torch.float32)
@@ -126,10 +125,7 @@ class LatentAttention:
         q_lat = rt.ws.buffer("latent_q_abs", (n, heads * (rank + rot)), torch.float32)
         ops.latent_queries(q_lat, q, self.w_uk, table, heads, dim, rot, rank, self.scale, batch)
         mixed = rt.ws.buffer("latent_mixed", (n, heads * rank), torch.float32)
-        if tiles is not None:
-            ops.latent_attention_tiled(mixed, q_lat, None, None, 0, cache, heads, rank, rot, batch)
-        else:
-            ops.latent_attention(mixed, q_lat, cache, heads, rank, rot, batch)
+        ops.latent_attention(mixed, q_lat, cache, heads, rank, rot, batch)
         ops.latent_values(attended, mixed, self.w_uv, gates, gate_at, heads, rank, vdim)
         ops.gemm(residual, attended, self.w_o, epilogue)
 

@@ -195,6 +195,8 @@ class ActivationExperts:
 
     def kernel_libraries(self, rt) -> set[str]:
         names = {"moe", "elementwise"}
+        if rt.dtype == torch.bfloat16 and self.hidden_size % 8 == 0 and self.intermediate_size % 8 == 0:
+            names.add("moe_grouped")
         if self.shared is not None and hasattr(self.shared, "kernel_libraries"):
             names |= set(self.shared.kernel_libraries(rt))
         return names
