@@ -664,7 +664,9 @@ DLLM_EXPORT int dllm_concat_restart(void* both, float* x, const float* kept, con
 // normed rows of tokens before the step come from `history` [slots, n_taps - 1, hidden] (float32, the oldest first),
 // those of the step are normed again here from the stream (a row's norm costs one pass over it). A block per token;
 // everything float32, rounded once to the output type. In a step of single tokens the block also moves the history
-// on; otherwise `norm_conv_history_kernel` does, after every block has read the old one.
+// on; otherwise `norm_conv_history_kernel` does, after every block has read the old one. A step of few tokens deals
+// each token's channels to several blocks (blockIdx.y; every one of them sums the row's squares for itself), so that
+// a block's loads of history, taps and weights are one round and not a chain of them.
 #define CONV_MAX_TAPS 8
 
 template <typename T>
@@ -690,7 +692,7 @@ __global__ void __launch_bounds__(256) norm_conv_kernel(T* __restrict__ out, con
   }
   __syncthreads();
   float* old = history + (size_t)slot * kept * hidden;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < hidden; i += gridDim.y * blockDim.x) {
     float h[CONV_MAX_TAPS];  // h[j]: the input `kept - j` tokens back
     for (int j = 0; j < n_taps; ++j) {
       int back = kept - j;
@@ -745,12 +747,15 @@ DLLM_EXPORT int dllm_norm_conv(void* out, const float* x, const float* w, const 
   if (!out || !x || !w || !taps || !tok_seq || !cu_seqlens || !slots || (n_taps > 1 && !history))
     return DLLM_BAD_ARGUMENT;
   int threads = hidden >= 1024 ? 256 : 128;
+  int slices = 1;
+  if (tokens <= 64) slices = (hidden + threads - 1) / threads < 32 ? (hidden + threads - 1) / threads : 32;
+  dim3 grid(tokens, slices);
   int status;
   if (out_dtype == DLLM_F32)
-    status = dllm_launch_pdl(norm_conv_kernel<float>, dim3(tokens), dim3(threads), 0, stream, (float*)out, x, w, taps,
+    status = dllm_launch_pdl(norm_conv_kernel<float>, grid, dim3(threads), 0, stream, (float*)out, x, w, taps,
                              n_taps, history, tok_seq, cu_seqlens, slots, hidden, eps, single);
   else if (out_dtype == DLLM_BF16)
-    status = dllm_launch_pdl(norm_conv_kernel<__nv_bfloat16>, dim3(tokens), dim3(threads), 0, stream,
+    status = dllm_launch_pdl(norm_conv_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream,
                              (__nv_bfloat16*)out, x, w, taps, n_taps, history, tok_seq, cu_seqlens, slots, hidden, eps,
                              single);
   else

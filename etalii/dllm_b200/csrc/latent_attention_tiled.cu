@@ -82,7 +82,8 @@ __global__ void __launch_bounds__(THREADS) latent_tiled_kernel(TiledArgs a) {
   const int b = blockIdx.y;
   const int tok0 = a.cu_seqlens[b], n_new = a.cu_seqlens[b + 1] - tok0;
   const long long pairs = (long long)n_new * heads;
-  const long long p0 = (long long)blockIdx.x * BM;
+  // (the last rows of a sequence see the most keys: they go first, so that the longest blocks do not end the kernel)
+  const long long p0 = (long long)(gridDim.x - 1 - blockIdx.x) * BM;
   if (p0 >= pairs) return;
   const int rows = (int)min((long long)BM, pairs - p0);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
