@@ -663,9 +663,9 @@ def latent_tiles(dtype, rank: int, rot: int, page_size: int = 64):
 
 def latent_splits(batch, heads: int) -> int:
     """Over how many blocks the tile kernel deals a sequence's keys: one where the step's rows fill the
-    multiprocessors by themselves, else enough for two blocks each, every block with 128 positions or more."""
+    multiprocessors by themselves, else enough for two blocks each, every block with 64 positions or more."""
     blocks = batch.n_seqs * (-(-batch.max_new * heads // 64))
-    return max(1, min(64, 296 // max(1, blocks), batch.max_context // 128))
+    return max(1, min(64, 296 // max(1, blocks), batch.max_context // 64))
 
 
 def latent_attention_tiled(out: torch.Tensor, q: torch.Tensor, table: torch.Tensor | None, gates: torch.Tensor | None,
