@@ -317,7 +317,7 @@ def _shape(heads, dim, rot_dim, vdim, q_rank, kv_rank, base=1e4, scale=0.25):
 LATENT_SHAPES = {
     "unequal": _shape(3, 16, 8, 24, 40, 32),
     "one_head": _shape(1, 8, 2, 16, 8, 24, base=50.0, scale=0.5),
-    "tiles": _shape(8, 64, 32, 64, 96, 128, base=1e6, scale=0.1),
+    "tiles": _shape(6, 48, 16, 40, 80, 128, base=1e5, scale=0.12),
     "nothing_rotated": _shape(2, 20, 0, 12, 24, 40, scale=0.3),
     "wide_latent": _shape(4, 32, 64, 16, 48, 256, scale=0.08),
     "heads_across_tiles": _shape(40, 16, 16, 8, 32, 64, scale=0.2),  # a token's heads do not fill whole 64-row tiles
@@ -493,7 +493,7 @@ def _plain_memory(w, p, h, eps=1e-5):
 
 MEMORY_SHAPES = [dict(heads=2, dim=20, vdim=12, gate_cap=8.0), dict(heads=1, dim=6, vdim=24, gate_cap=3.0),
                  dict(heads=3, dim=64, vdim=40, gate_cap=15.0), dict(heads=4, dim=132, vdim=16, gate_cap=30.0),
-                 dict(heads=6, dim=32, vdim=128, gate_cap=15.0)]
+                 dict(heads=5, dim=32, vdim=128, gate_cap=12.0)]
 
 
 @pytest.mark.parametrize("name,dtype", DTYPES)
