@@ -89,9 +89,13 @@ __global__ void __launch_bounds__(THREADS) latent_tiled_kernel(TiledArgs a) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int first_pos = a.tok_pos[tok0];  // positions of a sequence's new tokens are consecutive
 
-  // shared memory starts as zeros: rows beyond the tile, places beyond rank + rot
-  for (int i = tid; i < (BM + 2 * BN) * ld / 8; i += THREADS) reinterpret_cast<uint4*>(smem_raw)[i] = make_uint4(0, 0, 0, 0);
-  __syncthreads();
+  // the places of a shared-memory row behind rank + rot are zeros in queries and keys (nothing else writes them);
+  // rows beyond the tile's own keep what they hold: their scores are masked, their sums never stored
+  {
+    const int pad = ld - width;
+    for (int i = tid; i < (BM + 2 * BN) * pad; i += THREADS)
+      q_s[(size_t)(i / pad) * ld + width + i % pad] = __float2bfloat16_rn(0.f);
+  }
 
   const int* pages = a.page_table + (size_t)a.slots[b] * a.max_pages;
   const int pieces = width >> 3;
@@ -122,21 +126,29 @@ __global__ void __launch_bounds__(THREADS) latent_tiled_kernel(TiledArgs a) {
   load_keys(0, kt_begin);
   cp_async_commit();
 
-  // the queries, rotated where that is still to do, as bfloat16
+  // the queries, rotated where that is still to do, as bfloat16 (four places a thread: rank and rot are even, rank +
+  // rot a multiple of 8)
   {
     const float* src = a.q + ((size_t)tok0 * heads + p0) * width;
-    const int half = a.rot >> 1, rank = a.rank;
-    for (int idx = tid; idx < rows * width; idx += THREADS) {
-      int r = idx / width, c = idx - r * width;
-      float v = src[idx];
-      if (a.table != nullptr && c >= rank) {
-        int i = c - rank, pos = first_pos + (int)((p0 + r) / heads);
-        int pair = i < half ? i : i - half;
-        const float* cs = a.table + ((size_t)pos * half + pair) * 2;
-        float other = src[idx + (i < half ? half : -half)];
-        v = i < half ? v * cs[0] - other * cs[1] : v * cs[0] + other * cs[1];
+    const int half = a.rot >> 1, rank = a.rank, quads = width >> 2;
+    for (int idx = tid; idx < rows * quads; idx += THREADS) {
+      int r = idx / quads, c = (idx - r * quads) * 4;
+      const float* at = src + (size_t)r * width + c;
+      float4 v4 = *reinterpret_cast<const float4*>(at);
+      float v[4] = {v4.x, v4.y, v4.z, v4.w};
+      if (a.table != nullptr && c + 3 >= rank) {
+        int pos = first_pos + (int)((p0 + r) / heads);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          int i = c + e - rank;
+          if (i < 0) continue;
+          int pair = i < half ? i : i - half;
+          const float* cs = a.table + ((size_t)pos * half + pair) * 2;
+          float other = at[e + (i < half ? half : -half)];
+          v[e] = i < half ? v[e] * cs[0] - other * cs[1] : v[e] * cs[0] + other * cs[1];
+        }
       }
-      q_s[(size_t)r * ld + c] = __float2bfloat16_rn(v);
+      *reinterpret_cast<uint2*>(q_s + (size_t)r * ld + c) = make_uint2(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]));
     }
   }
 
@@ -288,27 +300,44 @@ __global__ void __launch_bounds__(THREADS) latent_tiled_kernel(TiledArgs a) {
 }
 
 // A block per (token, head) pair: the splits' sums weighted by 2^(their maximum - the largest), divided by the total.
+// The first 64 threads take a split each (weights and total through shared memory), then a thread a column.
 __global__ void __launch_bounds__(128) latent_combine_kernel(TiledArgs a, long long pairs) {
+  __shared__ float weight[64];
+  __shared__ float scratch[4];
   pdl_launch_dependents();
   pdl_wait();
   const long long p = blockIdx.x;
   if (p >= pairs) return;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const float* ml = a.part_ml + (size_t)p * a.splits * 2;
-  float top = -INFINITY;
-  for (int z = 0; z < a.splits; ++z) top = fmaxf(top, ml[2 * z]);
-  float total = 0.f;
-  for (int z = 0; z < a.splits; ++z)
-    if (ml[2 * z] != -INFINITY) total += fast_exp2(ml[2 * z] - top) * ml[2 * z + 1];
-  float factor = 1.0f / total;
+  float m = -INFINITY, l = 0.f;
+  if (tid < a.splits) {
+    m = ml[2 * tid];
+    l = ml[2 * tid + 1];
+  }
+  float top = warp_max(m);
+  if (lane == 0) scratch[warp] = top;
+  __syncthreads();
+  top = fmaxf(fmaxf(scratch[0], scratch[1]), fmaxf(scratch[2], scratch[3]));
+  float w = m == -INFINITY ? 0.f : fast_exp2(m - top);
+  if (tid < 64) weight[tid] = w;
+  float total = warp_sum(w * l);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = total;
+  __syncthreads();
+  float factor = 1.0f / (scratch[0] + scratch[1] + scratch[2] + scratch[3]);
   if (a.gates != nullptr) {
     float z = a.gates[(size_t)(p / a.heads) * a.gate_ld + (int)(p % a.heads)];
     factor *= z >= 0.f ? 1.0f / (1.0f + expf(-z)) : expf(z) / (1.0f + expf(z));
   }
   const float* o = a.part_o + (size_t)p * a.splits * a.rank;
-  for (int d = threadIdx.x; d < a.rank; d += blockDim.x) {
+  for (int d = tid; d < a.rank; d += blockDim.x) {
     float sum = 0.f;
-    for (int z = 0; z < a.splits; ++z)
-      if (ml[2 * z] != -INFINITY) sum = fmaf(fast_exp2(ml[2 * z] - top), o[(size_t)z * a.rank + d], sum);
+#pragma unroll 8
+    for (int z = 0; z < a.splits; ++z) {
+      float wz = weight[z];
+      if (wz != 0.f) sum = fmaf(wz, o[(size_t)z * a.rank + d], sum);  // (a split without keys wrote no sums)
+    }
     sum *= factor;
     if (a.out_bf16) ((bf16*)a.out)[(size_t)p * a.rank + d] = __float2bfloat16_rn(sum);
     else ((float*)a.out)[(size_t)p * a.rank + d] = sum;
