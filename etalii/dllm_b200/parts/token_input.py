@@ -54,7 +54,10 @@ class GatedTokenInput:
             operand = rt.ws.buffer("stream_operand", tuple(x.shape), rt.dtype)
             ops.cast_rows(operand, x)
         z = rt.ws.buffer("token_gate", (n, self.dim), torch.float32)
-        ops.gemm(z, operand, self.w_gate, ops.EPI_STORE_F32)
+        # (few rows of a long reduction: a block per 16 weight rows would be a handful of blocks, so the reduction is
+        # split over the blocks of a cluster)
+        narrow = rt.dtype == torch.bfloat16 and n <= 16 and self.dim <= 256 and self.hidden_size >= 1024
+        ops.gemm(z, operand, self.w_gate, ops.EPI_STORE_F32, kernel=6 if narrow else 0)
         gated = rt.ws.buffer("token_gated", (n, self.padded), rt.dtype)
         ops.gate_embed(gated, z, self.table, self.offset, self.dim, batch.tokens, ops.ACTIVATIONS[self.activation])
         y = rt.ws.buffer("sublayer_out", tuple(x.shape), torch.float32)
