@@ -62,6 +62,14 @@ CASES = {
                mlp=moe(ff=8, experts=2, top=2, shared_ff=8)),
         memory(heads=1, dim=6, vdim=24, gate_cap=3.0, mlp=None)], width=64, vocab=97, eps=3e-4, taps=1, side_dim=8,
         loop=(0, 2, 1)),
+    # five heads over a latent of 72 (padded to 128 in the tile kernel), three memory heads of 12, seven experts, three
+    # taps, a single layer run three times in the middle
+    "uneven": lambda: config([
+        memory(heads=3, dim=12, vdim=40, gate_cap=5.0, mlp=dense(56)),
+        latent(heads=5, dim=24, rot_dim=8, vdim=40, q_rank=56, kv_rank=72, scale=0.18, base=3e4,
+               mlp=moe(ff=40, experts=7, top=3, shared_ff=24)),
+        latent(heads=2, dim=40, rot_dim=24, vdim=12, q_rank=16, kv_rank=16, scale=0.12, mlp=dense(24))],
+        width=88, vocab=301, taps=3, side_dim=20, loop=(1, 2, 3)),
 }
 
 
