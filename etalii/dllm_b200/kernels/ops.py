@@ -655,10 +655,15 @@ def latent_values(out: torch.Tensor, mixed: torch.Tensor, uv: torch.Tensor, gate
 
 def latent_tiles(dtype, rank: int, rot: int, page_size: int = 64):
     """The padded rank the tensor-core kernel runs a latent of these sizes with, or None where only the general kernel
-    runs: float32, a rank above 256, rows that are no whole 16-byte pieces, pages that are no multiple of 32."""
+    runs: float32, a rank above 256, rows that are no whole 16-byte pieces or too long for a block's shared memory,
+    pages that are no multiple of 32."""
     if dtype != torch.bfloat16 or rank > 256 or rank % 8 or (rank + rot) % 8 or rot % 2 or page_size % 32:
         return None
-    return 64 if rank <= 64 else (128 if rank <= 128 else 256)
+    padded = 64 if rank <= 64 else (128 if rank <= 128 else 256)
+    row = max(-(-(rank + rot) // 16) * 16, padded) + 8  # values of a shared-memory row
+    if 128 * row * 2 > 200 * 1024:  # (64 query rows and two stages of 32 keys)
+        return None
+    return padded
 
 
 def latent_splits(batch, heads: int) -> int:
