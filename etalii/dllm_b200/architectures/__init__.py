@@ -1,1 +1,1 @@
-from . import llama, revupel, satavik, tisalorn  # noqa: F401  (register the architectures)
+from . import gaperax, llama, revupel, satavik, tisalorn  # noqa: F401  (register the architectures)

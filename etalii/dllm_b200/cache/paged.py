@@ -31,6 +31,7 @@ from .allocators import CacheError, FreeList
 class CacheNeed:
     """What one cache entry needs. kind "kv": keys and values of `kv_heads` x `head_dim` per position (values of
     `value_dim` where that is given and differs), all of them (window None), the last `window`, or those of the
+    last `window` and the first `keep_first` (a window that also keeps a sequence's start), or those of the
     running chunk of `chunk` positions (a mixer whose tokens only look back to the start of their own chunk: positions
     of chunks that are over are never read again; several mixers that read one entry with chunks of their own give a
     tuple of sizes, and a position is kept while any of them can still see it). With `keys_only` a position holds one
@@ -48,6 +49,9 @@ class CacheNeed:
     value_dim: int = 0
     chunk: int | tuple[int, ...] | None = None
     keys_only: bool = False
+    keep_first: int = 0
+    """With a window: the sequence's first `keep_first` positions stay visible at any distance, so the pages that
+    hold them are kept while the window moves on."""
 
     def chunks(self) -> tuple[int, ...]:
         if not self.chunk:
@@ -143,7 +147,7 @@ class PagedCache:
                 # A windowed group holds at most the window (plus the page being filled) per sequence while it
                 # decodes; but a whole prompt enters in one step and needs all its positions at once, so there is
                 # room for one sequence of the longest length on top of every slot's window.
-                per_sequence = -(-need.window // self.page_size) + 1
+                per_sequence = -(-need.window // self.page_size) + 1 + -(-need.keep_first // self.page_size)
                 pages = min(self.n_pages, per_sequence * self.n_slots + -(-self.max_length // self.page_size))
             group = _KvGroup(need, entries, pages, self.n_slots, self.max_pages, self.page_size, dtype, device)
             self._groups.append(group)
@@ -193,7 +197,8 @@ class PagedCache:
                 start = min((self.lengths[slot] // size) * size for size in group.need.chunks())
                 first_needed = max(first_needed, start // self.page_size)
             if first_needed:
-                for index in range(min(first_needed, len(have))):
+                kept = -(-group.need.keep_first // self.page_size) if group.need.window else 0
+                for index in range(kept, min(first_needed, len(have))):
                     if have[index] is not None:
                         group.pool.give([have[index]])
                         have[index] = None

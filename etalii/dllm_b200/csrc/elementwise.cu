@@ -869,3 +869,75 @@ DLLM_EXPORT int dllm_gate_embed(void* out, const float* z, int stride, const voi
                            kind, status);
   return DLLM_BAD_ARGUMENT;
 }
+
+// ---- a norm without statistics ---------------------------------------------------------------------------------------
+// out[r, i] = tanh(alpha * x[row(r), i]) * weight[i] + bias[i] in float32, rounded once to the output type; row(r) =
+// rows[r] where `rows` is given (a gather of the wanted rows), else r. Four values a thread where rows start on 16
+// bytes.
+template <typename T>
+__global__ void __launch_bounds__(256) dynamic_tanh_kernel(T* __restrict__ out, const float* __restrict__ x,
+                                                           const float* __restrict__ weight,
+                                                           const float* __restrict__ bias,
+                                                           const int* __restrict__ rows, int hidden, float alpha) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int r = blockIdx.x;
+  const float* src = x + (size_t)(rows ? rows[r] : r) * hidden;
+  T* dst = out + (size_t)r * hidden;
+  if ((hidden & 3) == 0) {
+    for (int i = (blockIdx.y * blockDim.x + threadIdx.x) * 4; i < hidden; i += gridDim.y * blockDim.x * 4) {
+      float4 v = *reinterpret_cast<const float4*>(src + i), w = *reinterpret_cast<const float4*>(weight + i),
+             b = *reinterpret_cast<const float4*>(bias + i);
+      store4(dst + i, fmaf(tanhf(alpha * v.x), w.x, b.x), fmaf(tanhf(alpha * v.y), w.y, b.y),
+             fmaf(tanhf(alpha * v.z), w.z, b.z), fmaf(tanhf(alpha * v.w), w.w, b.w));
+    }
+    return;
+  }
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < hidden; i += gridDim.y * blockDim.x)
+    dst[i] = from_float<T>(fmaf(tanhf(alpha * src[i]), weight[i], bias[i]));
+}
+
+DLLM_EXPORT int dllm_dynamic_tanh(void* out, const float* x, const float* weight, const float* bias, const int* rows,
+                                  int n_rows, int hidden, float alpha, int out_dtype, cudaStream_t stream) {
+  if (n_rows <= 0) return DLLM_OK;
+  if (hidden <= 0 || !out || !x || !weight || !bias) return DLLM_BAD_ARGUMENT;
+  int across = (hidden + 1023) / 1024;
+  dim3 grid(n_rows, across > 64 ? 64 : across);
+  if (out_dtype == DLLM_F32)
+    return dllm_launch_pdl(dynamic_tanh_kernel<float>, grid, dim3(256), 0, stream, (float*)out, x, weight, bias, rows,
+                           hidden, alpha);
+  if (out_dtype == DLLM_BF16)
+    return dllm_launch_pdl(dynamic_tanh_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, (__nv_bfloat16*)out, x,
+                           weight, bias, rows, hidden, alpha);
+  return DLLM_BAD_ARGUMENT;
+}
+
+// ---- gated unit with an activation by kind ---------------------------------------------------------------------------
+// in[r] = gate_0, up_0, gate_1, up_1, ... float32, as the product of the interleaved weight left them;
+// out[r, i] = act(gate_i) * up_i (kinds as `activate`), computed in float32, rounded once.
+template <typename T>
+__global__ void __launch_bounds__(256) glu_act_kernel(T* __restrict__ out, const float* __restrict__ in,
+                                                      long long total, int kind) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    float2 v = *reinterpret_cast<const float2*>(in + 2 * i);
+    out[i] = from_float<T>(activate(v.x, kind) * v.y);
+  }
+}
+
+DLLM_EXPORT int dllm_glu_act(void* out, const float* in, int rows, int width, int kind, int out_dtype,
+                             cudaStream_t stream) {
+  if (rows <= 0) return DLLM_OK;
+  if (width <= 0 || kind < 0 || kind > 3) return DLLM_UNSUPPORTED_SIZE;
+  if (!out || !in) return DLLM_BAD_ARGUMENT;
+  long long total = (long long)rows * width;
+  int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  if (out_dtype == DLLM_F32)
+    return dllm_launch_pdl(glu_act_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)out, in, total, kind);
+  if (out_dtype == DLLM_BF16)
+    return dllm_launch_pdl(glu_act_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (__nv_bfloat16*)out, in,
+                           total, kind);
+  return DLLM_BAD_ARGUMENT;
+}

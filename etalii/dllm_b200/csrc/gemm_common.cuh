@@ -26,6 +26,9 @@
 // with g = min(gate, limit), u = clamp(up, -limit, limit), `limit` a launch argument. The weight-streaming kernels
 // (at most 64 rows) have it; larger steps store gate and up and apply `glu_clamped_kernel`.
 #define EPI_GLU_CLAMPED 10
+// W's rows interleave gate and up; C in the activation type [M,N/2] = gelu(gate) * up with the tanh form of gelu,
+// 0.5 g (1 + tanh(sqrt(2 / pi) (g + 0.044715 g^3))), in float32. Where EPI_GLU_CLAMPED is: the weight-streaming kernels.
+#define EPI_GLU_GELU_TANH 11
 
 // What the q/k/v epilogue needs: where queries go, where the cache is, the rotation table, who the tokens are.
 struct RopeArgs {
@@ -103,6 +106,10 @@ __device__ __forceinline__ float glu_clamped(float gate, float up, float limit) 
   return g * (1.0f / (1.0f + expf(-1.702f * g))) * (u + 1.0f);
 }
 
+__device__ __forceinline__ float gelu_tanh_f32(float g) {
+  return 0.5f * g * (1.0f + tanhf(0.79788456080286535588f * (g + 0.044715f * g * g * g)));
+}
+
 template <int EPI, typename T>
 __device__ __forceinline__ void epilogue_pair(void* __restrict__ c, int m, int n, int M, int N, float v0, float v1,
                                               float limit = 0.f) {
@@ -123,6 +130,9 @@ __device__ __forceinline__ void epilogue_pair(void* __restrict__ c, int m, int n
   } else if (EPI == EPI_GLU_CLAMPED) {
     T* dst = (T*)c + (size_t)m * (N / 2) + (n >> 1);
     dst[0] = from_float<T>(glu_clamped(v0, v1, limit));
+  } else if (EPI == EPI_GLU_GELU_TANH) {
+    T* dst = (T*)c + (size_t)m * (N / 2) + (n >> 1);
+    dst[0] = from_float<T>(gelu_tanh_f32(v0) * v1);
   } else {
     T* dst = (T*)c + (size_t)m * (N / 2) + (n >> 1);
     dst[0] = from_float<T>(silu_for<T>(v0) * v1);

@@ -388,6 +388,7 @@ int dispatch(void* c, const void* a, const float* norm_w, float eps, const bf16*
     case EPI_SWIGLU: return launch<EPI_SWIGLU, NORM>(c, a, norm_w, eps, w, M, N, K, rope, pf, blocks, stream);
     case EPI_QKV_ROPE: return launch<EPI_QKV_ROPE, NORM>(c, a, norm_w, eps, w, M, N, K, rope, pf, blocks, stream);
     case EPI_GLU_CLAMPED: return launch<EPI_GLU_CLAMPED, NORM>(c, a, norm_w, eps, w, M, N, K, rope, pf, blocks, stream);
+    case EPI_GLU_GELU_TANH: return launch<EPI_GLU_GELU_TANH, NORM>(c, a, norm_w, eps, w, M, N, K, rope, pf, blocks, stream);
     default: return DLLM_BAD_ARGUMENT;
   }
 }
@@ -401,9 +402,10 @@ DLLM_EXPORT int dllm_gemv_cluster(void* c, const void* a, const float* norm_w, f
                                   int K, int epilogue, int cluster, const void* prefetch_ptr, long long prefetch_bytes,
                                   cudaStream_t stream) {
   if (M <= 0 || N <= 0) return DLLM_OK;
-  bool gated = epilogue == EPI_SWIGLU || epilogue == EPI_GLU_CLAMPED;
+  bool gated = epilogue == EPI_SWIGLU || epilogue == EPI_GLU_CLAMPED || epilogue == EPI_GLU_GELU_TANH;
   if (M > 64 || K <= 0 || (K & 7) || ((N & 1) && gated) || epilogue < 0 ||
-      (epilogue > EPI_SWIGLU && epilogue != EPI_GLU_CLAMPED) || (epilogue == EPI_GLU_CLAMPED && norm_w != nullptr))
+      (epilogue > EPI_SWIGLU && epilogue != EPI_GLU_CLAMPED && epilogue != EPI_GLU_GELU_TANH) ||
+      (epilogue == EPI_GLU_CLAMPED && norm_w != nullptr))
     return DLLM_UNSUPPORTED_SIZE;
   if (cluster < 0) return DLLM_BAD_ARGUMENT;
   int blocks = cluster;

@@ -8,7 +8,8 @@
 //                    the up projection, the key latent normed and r rotated into the token's place in the cache.
 //   latent_queries:  per (token, head): [ W_uk,h^T q_plain | rotate(q_rot) ] * scale, float32.
 //   latent_attention: causal softmax attention of every (token, head) over its sequence's rows; the general kernel, a
-//                    warp per pair, float32 arithmetic whatever the cache's type.
+//                    warp per pair, float32 arithmetic whatever the cache's type. With `sinks` the softmax's
+//                    denominator also holds exp(sinks[head]): a learned score per head that has no key and no value.
 //   latent_values:   per (token, head): W_uv,h (weighted sum of c) * sigmoid(gate), in the activation type.
 //
 // Cache layout (keys only): [page][row][rank + rot] in the cache's type; page_table[slot * max_pages + i] is the page
@@ -118,7 +119,8 @@ constexpr int MAX_COLS = 16;  // rank <= 32 * MAX_COLS
 template <typename T>
 __global__ void __launch_bounds__(ATT_WARPS * 32) latent_attention_kernel(
     const float* __restrict__ q, float* __restrict__ out, LatentCache cache, int heads, int rank,
-    const int* __restrict__ tok_seq, const int* __restrict__ tok_pos, const int* __restrict__ slots, int tokens) {
+    const int* __restrict__ tok_seq, const int* __restrict__ tok_pos, const int* __restrict__ slots, int tokens,
+    const float* __restrict__ sinks) {
   extern __shared__ float queries[];  // ATT_WARPS x width
   pdl_launch_dependents();
   pdl_wait();
@@ -135,7 +137,12 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) latent_attention_kernel(
   float acc[MAX_COLS];
 #pragma unroll
   for (int i = 0; i < MAX_COLS; ++i) acc[i] = 0.f;
+  // (a sink is a score without a key or a value that counts once in the denominator: the walk starts from it)
   float top = -INFINITY, total = 0.f;
+  if (sinks != nullptr) {
+    top = sinks[pair % heads];
+    total = 1.0f;
+  }
   for (int j0 = 0; j0 <= pos; j0 += 32) {
     const int j = j0 + lane;
     float score = -INFINITY;
@@ -240,7 +247,7 @@ DLLM_EXPORT int dllm_latent_queries(const float* q, const void* uk, const float*
 DLLM_EXPORT int dllm_latent_attention(const float* q, float* out, void* cache_base, const int* page_table,
                                       int max_pages, int page_size, int heads, int rank, int rot,
                                       const int* tok_seq, const int* tok_pos, const int* slots, int tokens,
-                                      int cache_dtype, cudaStream_t stream) {
+                                      int cache_dtype, const float* sinks, cudaStream_t stream) {
   if (tokens <= 0) return DLLM_OK;
   if (heads <= 0 || rank <= 0 || rank > 32 * MAX_COLS || rot < 0 || (size_t)(rank + rot) * ATT_WARPS * 4 > 48 * 1024)
     return DLLM_UNSUPPORTED_SIZE;
@@ -251,10 +258,10 @@ DLLM_EXPORT int dllm_latent_attention(const float* q, float* out, void* cache_ba
   size_t bytes = (size_t)ATT_WARPS * (rank + rot) * sizeof(float);
   if (cache_dtype == DLLM_F32)
     return dllm_launch_pdl(latent_attention_kernel<float>, grid, dim3(ATT_WARPS * 32), bytes, stream, q, out, cache,
-                           heads, rank, tok_seq, tok_pos, slots, tokens);
+                           heads, rank, tok_seq, tok_pos, slots, tokens, sinks);
   if (cache_dtype == DLLM_BF16)
     return dllm_launch_pdl(latent_attention_kernel<__nv_bfloat16>, grid, dim3(ATT_WARPS * 32), bytes, stream, q, out,
-                           cache, heads, rank, tok_seq, tok_pos, slots, tokens);
+                           cache, heads, rank, tok_seq, tok_pos, slots, tokens, sinks);
   return DLLM_BAD_ARGUMENT;
 }
 

@@ -56,6 +56,7 @@ struct TiledArgs {
   const float* q;      // [tokens, heads, rank + rot] float32
   const float* table;  // [positions, rot / 2, (cos, sin)], or null: the rotated part arrives rotated
   const float* gates;  // gates[token * gate_ld + head], or null
+  const float* sinks;  // sinks[head]: a score without key or value that counts once in the denominator, or null
   int gate_ld;
   void* out;           // [tokens, heads, rank]: float32, or bfloat16 with out_bf16
   int out_bf16;
@@ -164,6 +165,19 @@ __global__ void __launch_bounds__(THREADS) latent_tiled_kernel(TiledArgs a) {
   for (int i = 0; i < 2; ++i) {
     int r = warp * 16 + gq + 8 * i;
     row_pos[i] = r < rows ? first_pos + (int)((p0 + r) / heads) : -1;  // (a row beyond the tile sees nothing)
+  }
+  if (a.sinks != nullptr && kt_begin == 0) {
+    // the walk over the keys starts from the sink: running maximum = the sink, running sum = its own weight, 1 (the
+    // sum is kept in four parts a row that meet at the end: the first takes it); with the keys dealt to several
+    // blocks, the block of the first keys has it
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      int r = warp * 16 + gq + 8 * i;
+      if (r < rows) {
+        m_run[i] = a.sinks[(int)((p0 + r) % heads)] * LOG2E;
+        l_run[i] = tq == 0 ? 1.0f : 0.f;
+      }
+    }
   }
   const int warp_rows = min(16, rows - warp * 16);  // <= 0: the warp has no row
   const int warp_first_pos = warp_rows > 0 ? first_pos + (int)((p0 + warp * 16) / heads) : -1;
@@ -362,6 +376,7 @@ int launch(const TiledArgs& a, int tiles, int n_seqs, cudaStream_t stream) {
 // blocks beyond a sequence's own pairs leave at once). splits > 1: part_o [pairs, splits, rank] and part_ml [pairs,
 // splits, 2] float32 scratch, pairs = the step's tokens x heads.
 DLLM_EXPORT int dllm_latent_attention_tiled(const float* q, const float* table, const float* gates, int gate_ld,
+                                            const float* sinks,
                                             void* out, int out_bf16, const void* cache, const int* page_table,
                                             int max_pages, int page_size, int heads, int rank, int rot,
                                             const int* cu_seqlens, const int* tok_pos, const int* slots, int n_seqs,
@@ -376,7 +391,7 @@ DLLM_EXPORT int dllm_latent_attention_tiled(const float* q, const float* table, 
   int k_width = ((rank + rot + 15) / 16) * 16;
   int ld = (k_width > padded_rank ? k_width : padded_rank) + 8;
   if ((size_t)(BM + 2 * BN) * ld * sizeof(bf16) > 200 * 1024) return DLLM_UNSUPPORTED_SIZE;
-  TiledArgs a{q, rot > 0 ? table : nullptr, gates, gate_ld, out, out_bf16, (const bf16*)cache, page_table, max_pages,
+  TiledArgs a{q, rot > 0 ? table : nullptr, gates, sinks, gate_ld, out, out_bf16, (const bf16*)cache, page_table, max_pages,
               page_size, cu_seqlens, tok_pos, slots, heads, rank, rot, ld, splits, part_o, part_ml};
   if (splits < 1 || splits > 64 || (splits > 1 && (!part_o || !part_ml || pairs <= 0))) return DLLM_BAD_ARGUMENT;
   long long most = (long long)max_new * heads;

@@ -41,6 +41,7 @@ SOURCES = {
     "diff_attention_decode": "diff_attention_decode.cu",
     "latent_attention": "latent_attention.cu",
     "latent_attention_tiled": "latent_attention_tiled.cu",
+    "sigmoid_attention": "sigmoid_attention.cu",
     "moe": "moe.cu",
     "moe_grouped": "moe_grouped.cu",
     "sampling": "sampling.cu",

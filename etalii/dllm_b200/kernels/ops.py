@@ -16,7 +16,10 @@ EPI_GLU_CLAMPED = 10
 -limit, limit). Only the weight-streaming kernels have it (`glu_clamped_fuses`); `eps` carries the limit."""
 _DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
 _STATUS = {-1: "bad argument", -2: "unsupported size", -3: "kernel launch failed"}
-_EPILOGUE_NAMES = {0: "store_f32", 1: "store", 2: "residual", 3: "swiglu", 10: "glu_clamped"}
+EPI_GLU_GELU_TANH = 11
+"""Gate and up rows interleaved as for SwiGLU: c[M, N/2] = gelu(gate) * up with the tanh form of gelu. Where
+EPI_GLU_CLAMPED is: the weight-streaming kernels (`glu_clamped_fuses`)."""
+_EPILOGUE_NAMES = {0: "store_f32", 1: "store", 2: "residual", 3: "swiglu", 10: "glu_clamped", 11: "glu_gelu_tanh"}
 
 
 class KernelError(RuntimeError):
@@ -30,6 +33,17 @@ _prototypes = {
     ("elementwise", "dllm_rmsnorm"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p],
     ("elementwise", "dllm_layernorm"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p],
     ("elementwise", "dllm_glu_clamped"): [c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_float, c_int, c_void_p],
+    ("elementwise", "dllm_dynamic_tanh"): [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float,
+                                           c_int, c_void_p],
+    ("elementwise", "dllm_glu_act"): [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    ("sigmoid_attention", "dllm_sigmoid_prepare"): [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                                    c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float,
+                                                    c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
+                                                    c_void_p, c_int, c_int, c_int, c_void_p],
+    ("sigmoid_attention", "dllm_sigmoid_attention"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                                      c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                                      c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                                      c_int, c_int, c_void_p, c_int, c_void_p],
     ("elementwise", "dllm_norm_sum_residual"): [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float,
                                                 c_float, c_void_p],
     ("elementwise", "dllm_norm_add_residual"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p],
@@ -67,8 +81,10 @@ _prototypes = {
     ("latent_attention", "dllm_latent_queries"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                                   c_int, c_float, c_void_p, c_int, c_void_p],
     ("latent_attention", "dllm_latent_attention"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                                                    c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
-    ("latent_attention_tiled", "dllm_latent_attention_tiled"): [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
+                                                    c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p,
+                                                    c_void_p],
+    ("latent_attention_tiled", "dllm_latent_attention_tiled"): [c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                                                c_void_p, c_int,
                                                                 c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                                                 c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                                                 c_void_p, c_void_p, ctypes.c_longlong, c_void_p],
@@ -279,6 +295,99 @@ def layernorm(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, eps: flo
     _check(_fn("elementwise", "dllm_layernorm")(out.data_ptr(), x.data_ptr(), weight.data_ptr(),
                                                 rows.data_ptr() if rows is not None else None, n, x.shape[-1],
                                                 float(eps), _code(out.dtype), _stream()), "layernorm")
+
+
+def dynamic_tanh(out: torch.Tensor, x: torch.Tensor, alpha: float, weight: torch.Tensor, bias: torch.Tensor,
+                 rows: torch.Tensor | None = None) -> None:
+    """out[r] = tanh(alpha * x[rows[r]] if rows is given else x[r]) * weight + bias; x, weight and bias float32."""
+    _cuda(out, x, weight, bias, rows)
+    assert x.dtype == torch.float32 and weight.dtype == torch.float32 and bias.dtype == torch.float32
+    assert weight.numel() == x.shape[-1] and bias.numel() == x.shape[-1]
+    n = out.shape[0]
+    assert out.shape[-1] == x.shape[-1] and (rows is not None or x.shape[0] >= n)
+    assert rows is None or (rows.dtype == torch.int32 and rows.numel() >= n)
+    _check(_fn("elementwise", "dllm_dynamic_tanh")(out.data_ptr(), x.data_ptr(), weight.data_ptr(), bias.data_ptr(),
+                                                   rows.data_ptr() if rows is not None else None, n, x.shape[-1],
+                                                   float(alpha), _code(out.dtype), _stream()), "dynamic_tanh")
+
+
+def glu_act(out: torch.Tensor, gate_up: torch.Tensor, activation: int) -> None:
+    """gate_up float32 [rows, 2 width] = gate_0, up_0, gate_1, up_1, ...; out[rows, width] = act(gate) * up in float32
+    (`activation`: a value of `ACTIVATIONS`), rounded once to out's type."""
+    _cuda(out, gate_up)
+    rows, width = out.shape
+    assert gate_up.shape == (rows, 2 * width) and gate_up.dtype == torch.float32
+    _check(_fn("elementwise", "dllm_glu_act")(out.data_ptr(), gate_up.data_ptr(), rows, width, int(activation),
+                                              _code(out.dtype), _stream()), "glu_act")
+
+
+def sigmoid_prepare(rows: torch.Tensor, q_at: int, k_at: int, v_at: int, q_out: torch.Tensor, cache, heads: int,
+                    biases, norm_weights, eps: float, batch, write_cache: bool = True) -> None:
+    """From a token's projected float32 row (q at q_at: heads x dim; k at k_at: kv_heads x dim; v at v_at: kv_heads x
+    value_dim): `biases` = (q, k, v) float32 vectors added first (None: no biases); `norm_weights` = (q, k) float32
+    weights of an RMS norm over the WHOLE q and the whole k, all heads at once (None: no norm). Queries go to q_out
+    (the cache's type), keys and values into the token's place in the cache."""
+    qb, kb, vb = biases if biases is not None else (None, None, None)
+    qw, kw = norm_weights if norm_weights is not None else (None, None)
+    _cuda(rows, q_out, qb, kb, vb, qw, kw)
+    dim, vdim, kv_heads = cache.head_dim, cache.value_dim, cache.kv_heads
+    assert rows.dtype == torch.float32 and q_out.dtype == cache.dtype and not cache.keys_only
+    assert q_out.shape[1] == heads * dim
+    for tensor, size in ((qb, heads * dim), (kb, kv_heads * dim), (vb, kv_heads * vdim), (qw, heads * dim),
+                         (kw, kv_heads * dim)):
+        assert tensor is None or (tensor.dtype == torch.float32 and tensor.numel() == size)
+    ptr = lambda tensor: tensor.data_ptr() if tensor is not None else None  # noqa: E731
+    _check(_fn("sigmoid_attention", "dllm_sigmoid_prepare")(
+        rows.data_ptr(), rows.shape[1], int(q_at), int(k_at), int(v_at), heads, kv_heads, dim, vdim, ptr(qb), ptr(kb),
+        ptr(vb), ptr(qw), ptr(kw), float(eps), q_out.data_ptr(), cache.base_ptr, cache.page_table.data_ptr(),
+        cache.max_pages, cache.page_size, batch.tok_seq.data_ptr(), batch.tok_pos.data_ptr(), batch.slots.data_ptr(),
+        batch.n_tokens, 1 if write_cache else 0, _code(cache.dtype), _stream()), "sigmoid_prepare")
+
+
+def sigmoid_attention_splits(batch, window: int, keep: int) -> int:
+    """Over how many blocks the general kernel deals a token's keys: one where the step's tokens fill the device by
+    themselves, else enough for about two blocks a multiprocessor, every block with two tiles of keys or more."""
+    reach = batch.max_context if window <= 0 else min(batch.max_context, window + keep + 32)
+    return max(1, min(296 // max(1, batch.n_tokens), reach // 64))
+
+
+def sigmoid_attention(out: torch.Tensor, q: torch.Tensor, cache, heads: int, scale: float, window: int, keep: int,
+                      mix: torch.Tensor | None, slopes: torch.Tensor | None, head_bias: torch.Tensor | None,
+                      gates: torch.Tensor | None, gate_at: int, batch, ws=None) -> None:
+    """Attention without a softmax over a cache of keys [dim] and values [value_dim]: token i weighs a visible key j
+    (j <= i and i - j < window, or j < keep; window 0: all) with sigmoid(q . k * scale - slopes[h] (i - j) +
+    head_bias[h]); `mix` float32 [heads, heads] then mixes the heads' weights, weight_h <- sum_g mix[h, g] weight_g;
+    head h applies its weights to the values of its kv head. out [tokens, heads x value_dim] in the cache's type, times
+    sigmoid(gates[t, gate_at + o]) where `gates` (float32 rows) is given. The general kernel: float32 arithmetic, either
+    cache type, every size up to heads x value_dim = 8192; with `ws` a step of few tokens deals each token's keys to
+    several blocks."""
+    _cuda(out, q, mix, slopes, head_bias, gates)
+    dim, vdim = cache.head_dim, cache.value_dim
+    assert q.dtype == cache.dtype and out.dtype == cache.dtype and not cache.keys_only
+    assert q.shape[1] == heads * dim and out.shape[1] == heads * vdim
+    assert mix is None or (mix.dtype == torch.float32 and tuple(mix.shape) == (heads, heads))
+    for tensor in (slopes, head_bias):
+        assert tensor is None or (tensor.dtype == torch.float32 and tensor.numel() == heads)
+    tokens = batch.n_tokens
+    splits = sigmoid_attention_splits(batch, window, keep) if ws is not None else 1
+    part = ws.buffer("sigmoid_part", (splits * tokens * heads * vdim,), torch.float32) if splits > 1 else None
+    gate_ptr = (gates.data_ptr() + 4 * int(gate_at)) if gates is not None else None
+    ptr = lambda tensor: tensor.data_ptr() if tensor is not None else None  # noqa: E731
+    _check(_fn("sigmoid_attention", "dllm_sigmoid_attention")(
+        q.data_ptr(), out.data_ptr(), cache.base_ptr, cache.page_table.data_ptr(), cache.max_pages, cache.page_size,
+        heads, cache.kv_heads, dim, vdim, ptr(mix), ptr(slopes), ptr(head_bias), gate_ptr,
+        gates.shape[1] if gates is not None else 0, float(scale), int(window), int(keep), batch.tok_seq.data_ptr(),
+        batch.tok_pos.data_ptr(), batch.slots.data_ptr(), tokens, splits, ptr(part), _code(cache.dtype), _stream()),
+        "sigmoid_attention", lambda: f"heads={heads} dim={dim} value_dim={vdim} page={cache.page_size}")
+
+
+SIGMOID_TILES_FROM = 16
+"""Steps of more tokens than this take the tensor-core form of the sigmoid attention where the sizes allow it."""
+
+
+def sigmoid_attention_tiles(dtype, heads: int, kv_heads: int, dim: int, vdim: int, page_size: int = 64) -> bool:
+    """Whether the tensor-core kernel runs these sizes."""
+    return False
 
 
 def glu_clamped_fuses(rows: int, outputs: int, inner: int) -> bool:
@@ -625,17 +734,21 @@ def latent_queries(out: torch.Tensor, q: torch.Tensor, uk: torch.Tensor, table: 
         dim, rot, rank, float(scale), batch.tok_pos.data_ptr(), _code(uk.dtype), _stream()), "latent_queries")
 
 
-def latent_attention(out: torch.Tensor, q: torch.Tensor, cache, heads: int, rank: int, rot: int, batch) -> None:
+def latent_attention(out: torch.Tensor, q: torch.Tensor, cache, heads: int, rank: int, rot: int, batch,
+                     sinks: torch.Tensor | None = None) -> None:
     """Causal softmax attention of every (token, head) over the rows [rank + rot] its sequence has cached: scores
     q . row (the queries carry the scale), out float32 [tokens, heads x rank] = the weighted sum of the rows' first
-    `rank` values. The general kernel: float32 arithmetic, either cache type, rank up to 512."""
-    _cuda(out, q)
+    `rank` values. With `sinks` (float32 [heads]) the softmax's denominator also holds exp(sinks[head]), a score that
+    has no key and no value. The general kernel: float32 arithmetic, either cache type, rank up to 512."""
+    _cuda(out, q, sinks)
+    assert sinks is None or (sinks.dtype == torch.float32 and sinks.numel() == heads)
     assert q.dtype == torch.float32 and out.dtype == torch.float32 and cache.head_dim == rank + rot
     assert q.shape[1] == heads * (rank + rot) and out.shape[1] == heads * rank
     _check(_fn("latent_attention", "dllm_latent_attention")(
         q.data_ptr(), out.data_ptr(), cache.base_ptr, cache.page_table.data_ptr(), cache.max_pages, cache.page_size,
         heads, rank, rot, batch.tok_seq.data_ptr(), batch.tok_pos.data_ptr(), batch.slots.data_ptr(), batch.n_tokens,
-        _code(cache.dtype), _stream()), "latent_attention", lambda: f"rank={rank} (at most 512)")
+        _code(cache.dtype), sinks.data_ptr() if sinks is not None else None, _stream()), "latent_attention",
+        lambda: f"rank={rank} (at most 512)")
 
 
 def latent_values(out: torch.Tensor, mixed: torch.Tensor, uv: torch.Tensor, gates: torch.Tensor | None, gate_at: int,
@@ -674,12 +787,15 @@ def latent_splits(batch, heads: int) -> int:
 
 
 def latent_attention_tiled(out: torch.Tensor, q: torch.Tensor, table: torch.Tensor | None, gates: torch.Tensor | None,
-                           gate_at: int, cache, heads: int, rank: int, rot: int, batch, ws=None) -> None:
+                           gate_at: int, cache, heads: int, rank: int, rot: int, batch, ws=None,
+                           sinks: torch.Tensor | None = None) -> None:
     """`latent_attention` on the tensor cores over a bfloat16 cache. q float32 [tokens, heads x (rank + rot)] in the
     latent's coordinates, scale included; with `table` its rotated parts are rotated on the way in. out [tokens,
     heads x rank]: float32, or bfloat16; with `gates` (float32 rows, head h at column gate_at + h) every head's sum
-    is multiplied by the sigmoid of its gate."""
-    _cuda(out, q, table, gates)
+    is multiplied by the sigmoid of its gate; with `sinks` (float32 [heads]) the softmax's denominator also holds
+    exp(sinks[head])."""
+    _cuda(out, q, table, gates, sinks)
+    assert sinks is None or (sinks.dtype == torch.float32 and sinks.numel() == heads)
     assert q.dtype == torch.float32 and out.dtype in (torch.float32, torch.bfloat16)
     assert cache.dtype == torch.bfloat16 and cache.keys_only and cache.kv_heads == 1 and cache.head_dim == rank + rot
     assert q.shape[1] == heads * (rank + rot) and out.shape[1] == heads * rank and out.is_contiguous()
@@ -693,7 +809,8 @@ def latent_attention_tiled(out: torch.Tensor, q: torch.Tensor, table: torch.Tens
     part_ml = ws.buffer("latent_part_ml", (pairs * splits * 2,), torch.float32) if splits > 1 else None
     _check(_fn("latent_attention_tiled", "dllm_latent_attention_tiled")(
         q.data_ptr(), table.data_ptr() if table is not None else None, gate_ptr,
-        gates.shape[1] if gates is not None else 0, out.data_ptr(), 1 if out.dtype == torch.bfloat16 else 0,
+        gates.shape[1] if gates is not None else 0, sinks.data_ptr() if sinks is not None else None, out.data_ptr(),
+        1 if out.dtype == torch.bfloat16 else 0,
         cache.base_ptr, cache.page_table.data_ptr(), cache.max_pages, cache.page_size, heads, rank, rot,
         batch.cu_seqlens.data_ptr(), batch.tok_pos.data_ptr(), batch.slots.data_ptr(), batch.n_seqs,
         int(batch.max_new), splits, part_o.data_ptr() if splits > 1 else None,
@@ -1132,8 +1249,8 @@ def gemm(c: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: int = EPI_
     m, k = a.shape
     n = w.shape[0]
     assert w.shape[1] == k, (a.shape, w.shape)
-    want_cols = n // 2 if epilogue in (EPI_SWIGLU, EPI_GLU_CLAMPED) else n
-    if epilogue == EPI_GLU_CLAMPED:
+    want_cols = n // 2 if epilogue in (EPI_SWIGLU, EPI_GLU_CLAMPED, EPI_GLU_GELU_TANH) else n
+    if epilogue in (EPI_GLU_CLAMPED, EPI_GLU_GELU_TANH):
         assert w.dtype == torch.bfloat16 and kernel == 0 and norm_weight is None and glu_clamped_fuses(m, n, k)
     want_dtype = torch.float32 if epilogue in (EPI_STORE_F32, EPI_RESIDUAL) else w.dtype
     assert tuple(c.shape) == (m, want_cols) and c.dtype == want_dtype, (c.shape, c.dtype, m, want_cols, want_dtype)

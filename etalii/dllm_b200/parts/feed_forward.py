@@ -182,6 +182,56 @@ class ActivationMLP:
         return {"gemv", "gemv_cluster", "gemm_tcgen05", "elementwise"}
 
 
+class GatedMLP:
+    """A gated feed-forward with the activation by name: down(act(gate(h)) * up(h)), without biases ("gelu_tanh": the
+    tanh form of gelu; "gelu": the erf form; "relu_squared"). Gate and up are one product whose rows interleave (row 2i
+    = gate_i, row 2i + 1 = up_i). A decode-sized bfloat16 step applies the activation in that product's epilogue (the
+    tanh form of gelu, which the weight-streaming kernels have built in); larger steps and float32 keep the product's
+    float32 rows and run the activation as a kernel of its own. The activation is computed in float32 either way."""
+
+    def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "gelu_tanh") -> None:
+        self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
+        if ops.ACTIVATIONS.get(activation, 0) == 0:
+            raise ValueError(f"activation {activation!r} is not known (gelu, gelu_tanh, relu_squared)")
+        self.activation = activation
+        self.w_gate_up = self.w_down = None
+
+    @staticmethod
+    def parameters(hidden_size, intermediate_size, **_) -> dict[str, ParamSpec]:
+        return {"gate": ParamSpec((intermediate_size, hidden_size)), "up": ParamSpec((intermediate_size, hidden_size)),
+                "down": ParamSpec((hidden_size, intermediate_size))}
+
+    def supports(self, rt) -> str | None:
+        return row_rule(rt, hidden_size=self.hidden_size, intermediate_size=self.intermediate_size)
+
+    def bind(self, tensors, rt) -> None:
+        gate, up = tensors["gate"].to(rt.dtype), tensors["up"].to(rt.dtype)
+        fused = torch.stack([gate, up], dim=1).reshape(2 * self.intermediate_size, self.hidden_size)
+        self.w_gate_up = fused.contiguous().to(rt.device)
+        self.w_down = rt.to_device(tensors["down"], rt.dtype)
+
+    def forward(self, h: torch.Tensor, residual: torch.Tensor, batch, rt, epilogue: int = ops.EPI_RESIDUAL) -> None:
+        """Adds into `residual` (float32), or with `epilogue=ops.EPI_STORE_F32` writes it."""
+        if isinstance(h, NormedInput):
+            h = h.tensor()
+        rows = h.shape[0]
+        act = rt.ws.buffer("ffn_act", (rows, self.intermediate_size), rt.dtype)
+        if rt.dtype == torch.bfloat16 and self.activation == "gelu_tanh" and \
+                ops.glu_clamped_fuses(rows, *self.w_gate_up.shape):
+            ops.gemm(act, h, self.w_gate_up, ops.EPI_GLU_GELU_TANH)
+        else:
+            both = rt.ws.buffer("ffn_gate_up_f32", (rows, 2 * self.intermediate_size), torch.float32)
+            ops.gemm(both, h, self.w_gate_up, ops.EPI_STORE_F32)
+            ops.glu_act(act, both, ops.ACTIVATIONS[self.activation])
+        ops.gemm(residual, act, self.w_down, epilogue)
+
+    def kernel_libraries(self, rt) -> set[str]:
+        if rt.dtype != torch.bfloat16:
+            return {"gemm_simt", "elementwise"}
+        return {"gemv", "gemv_cluster", "gemm_tcgen05", "elementwise"}
+
+
+register_part("feed_forward", "gated_mlp", GatedMLP)
 register_part("feed_forward", "swiglu", SwiGLU)
 register_part("feed_forward", "activation_mlp", ActivationMLP)
 register_part("feed_forward", "clamped_glu", ClampedGLU)

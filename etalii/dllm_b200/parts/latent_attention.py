@@ -3,9 +3,11 @@
 Per token, from the mixer's input h: the query goes through a latent of its own, c_q = rms(W_dq h) * w_q, q = W_uq c_q,
 laid out head by head as [dim plain | rot_dim rotated]. W_dkv h gives kv_rank + rot_dim numbers: the first kv_rank,
 divided by their root mean square and weighted, are the latent c; the last rot_dim, rotated by the position (pairs
-i, i + rot_dim / 2), are ONE key part r that all heads share. Head a has the keys [W_uk,a c | r] and the values
-W_uv,a c; the score is (q_plain . W_uk,a c + q_rot . r) * scale, causal, ordinary softmax; the head's output is
-multiplied by sigmoid(W_g h)_a and W_o runs over the concatenated heads.
+i, i + rot_dim / 2; a position encoding that pairs 2i with 2i + 1 has the rotated rows of W_uq and W_dkv put into that
+order once, when the weights are bound, which changes no q . k), are ONE key part r that all heads share. Head a has the keys [W_uk,a c | r] and the values
+W_uv,a c; the score is (q_plain . W_uk,a c + q_rot . r) * scale, causal, ordinary softmax (with `sink`, a learned
+number per head whose exponential also stands in the denominator: a score without a key or a value); the head's
+output is multiplied by sigmoid(W_g h)_a (with `gate`) and W_o runs over the concatenated heads.
 
 Only [c | r] is cached, one row per position for all heads (a keys-only cache entry). The kernels never build the
 heads' keys and values: since q_plain . W_uk c = (W_uk^T q_plain) . c, a query is taken into the latent's coordinates
@@ -33,11 +35,12 @@ from .spec import ParamSpec
 
 class LatentAttention:
     def __init__(self, hidden_size: int, num_heads: int, dim: int, rot_dim: int, vdim: int, q_rank: int, kv_rank: int,
-                 scale: float, eps: float, position=None, gate: bool = True) -> None:
+                 scale: float, eps: float, position=None, gate: bool = True, sink: bool = False) -> None:
         self.hidden_size, self.num_heads = int(hidden_size), int(num_heads)
         self.dim, self.rot_dim, self.vdim = int(dim), int(rot_dim), int(vdim)
         self.q_rank, self.kv_rank = int(q_rank), int(kv_rank)
-        self.scale, self.eps, self.gate = float(scale), float(eps), bool(gate)
+        self.scale, self.eps, self.gate, self.sink = float(scale), float(eps), bool(gate), bool(sink)
+        self.sinks = None
         if self.rot_dim and position is None:
             raise ValueError("a rotated key part needs a position encoding")
         self.position = build_part("position", position) if position is not None and self.rot_dim else None
@@ -48,7 +51,8 @@ class LatentAttention:
         self.w_qa = self.w_ov = None
 
     @staticmethod
-    def parameters(hidden_size, num_heads, dim, rot_dim, vdim, q_rank, kv_rank, gate=True, **_) -> dict[str, ParamSpec]:
+    def parameters(hidden_size, num_heads, dim, rot_dim, vdim, q_rank, kv_rank, gate=True, sink=False,
+                   **_) -> dict[str, ParamSpec]:
         heads = int(num_heads)
         out = {"dq": ParamSpec((int(q_rank), hidden_size)), "dq_norm": ParamSpec((int(q_rank),), "ones"),
                "uq": ParamSpec((heads * (int(dim) + int(rot_dim)), int(q_rank))),
@@ -58,6 +62,8 @@ class LatentAttention:
                "o": ParamSpec((hidden_size, heads * int(vdim)))}
         if gate:
             out["g"] = ParamSpec((heads, hidden_size))
+        if sink:
+            out["sink"] = ParamSpec((heads,))
         return out
 
     def supports(self, rt) -> str | None:
@@ -73,6 +79,20 @@ class LatentAttention:
 
     def bind(self, tensors, rt) -> None:
         # one product for everything a token needs of h: the two latents (with the shared key part) and the gates
+        tensors = dict(tensors)
+        order = self.position.row_order() if self.position is not None and hasattr(self.position, "row_order") \
+            else None
+        if order is not None:
+            # the position encoding pairs other places than the kernels rotate: the rotated rows of the two maps that
+            # make them are put in the kernels' order, the queries' and the shared key part's alike
+            index = torch.tensor(order, dtype=torch.long)
+            dkv, uq = tensors["dkv"], tensors["uq"]
+            tensors["dkv"] = torch.cat([dkv[:self.kv_rank], dkv[self.kv_rank:][index]], dim=0)
+            uq = uq.view(self.num_heads, self.dim + self.rot_dim, self.q_rank)
+            tensors["uq"] = torch.cat([uq[:, :self.dim], uq[:, self.dim:][:, index]], dim=1).reshape(
+                self.num_heads * (self.dim + self.rot_dim), self.q_rank).contiguous()
+        if self.sink:
+            self.sinks = tensors["sink"].to(torch.float32).contiguous().to(rt.device)
         names = ("dq", "dkv", "g") if self.gate else ("dq", "dkv")
         fused = torch.cat([tensors[name].to(rt.dtype) for name in names], dim=0)
         self.w_down = fused.contiguous().to(rt.device)
@@ -116,7 +136,8 @@ class LatentAttention:
             q_lat = rt.ws.buffer("latent_q_abs", (n, heads * (rank + rot)), torch.float32)
             ops.gemm(q_lat, cq, self.w_qa, ops.EPI_STORE_F32)
             mixed = rt.ws.buffer("latent_mixed16", (n, heads * rank), rt.dtype)
-            ops.latent_attention_tiled(mixed, q_lat, table, gates, gate_at, cache, heads, rank, rot, batch, rt.ws)
+            ops.latent_attention_tiled(mixed, q_lat, table, gates, gate_at, cache, heads, rank, rot, batch, rt.ws,
+                                       sinks=self.sinks)
             ops.gemm(residual, mixed, self.w_ov, epilogue)
             return
         q = rt.ws.buffer("latent_q", (n, heads * (dim + rot)), torch.float32)
@@ -125,7 +146,7 @@ class LatentAttention:
         q_lat = rt.ws.buffer("latent_q_abs", (n, heads * (rank + rot)), torch.float32)
         ops.latent_queries(q_lat, q, self.w_uk, table, heads, dim, rot, rank, self.scale, batch)
         mixed = rt.ws.buffer("latent_mixed", (n, heads * rank), torch.float32)
-        ops.latent_attention(mixed, q_lat, cache, heads, rank, rot, batch)
+        ops.latent_attention(mixed, q_lat, cache, heads, rank, rot, batch, sinks=self.sinks)
         ops.latent_values(attended, mixed, self.w_uv, gates, gate_at, heads, rank, vdim)
         ops.gemm(residual, attended, self.w_o, epilogue)
 

@@ -119,6 +119,34 @@ class LayerNorm:
         return out
 
 
+class DynamicTanh:
+    """A norm that computes no statistics: out = tanh(alpha x) * weight + bias, element by element in float32 from the
+    float32 residual stream, alpha ONE learned number (a tensor without dimensions in the checkpoint). Nothing of it
+    can move into the next product's weights (the tanh sits between), so its consumers get the finished rows."""
+
+    def __init__(self, hidden_size: int) -> None:
+        self.hidden_size = int(hidden_size)
+        self.weight = self.bias = None
+        self.alpha = 1.0
+
+    @staticmethod
+    def parameters(hidden_size: int) -> dict[str, ParamSpec]:
+        return {"weight": ParamSpec((int(hidden_size),), "ones"), "bias": ParamSpec((int(hidden_size),)),
+                "alpha": ParamSpec((), "ones")}
+
+    def bind(self, tensors, rt) -> None:
+        self.weight = rt.to_device(tensors["weight"], torch.float32)
+        self.bias = rt.to_device(tensors["bias"], torch.float32)
+        self.alpha = float(tensors["alpha"].to(torch.float32).reshape(()).item())
+
+    def forward(self, x: torch.Tensor, rt, rows: torch.Tensor | None = None, n_rows: int | None = None,
+                name: str = "normed") -> torch.Tensor:
+        n = x.shape[0] if rows is None else int(n_rows)
+        out = rt.ws.buffer(name, (n, self.hidden_size), rt.dtype)
+        ops.dynamic_tanh(out, x, self.alpha, self.weight, self.bias, rows)
+        return out
+
+
 FUSE_NORM_LIMIT = 16 << 20
 """Weights up to this many bytes take the norm inside their decode-sized product (one kernel less); with larger
 weights every block of the product would redo the norm of all rows, and a separate norm kernel is cheaper."""
@@ -152,3 +180,4 @@ def project(out: torch.Tensor, h, w: torch.Tensor, epilogue: int) -> None:
 
 register_part("norm", "rmsnorm", RMSNorm)
 register_part("norm", "layernorm", LayerNorm)
+register_part("norm", "dynamic_tanh", DynamicTanh)

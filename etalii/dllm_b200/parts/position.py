@@ -33,9 +33,33 @@ def rotary_frequencies(rotary_dim: int, theta: float, scaling: Mapping | None) -
                 smooth = (original / wavelength - low) / (high - low)
                 out.append((1 - smooth) * f / factor + smooth * f)
         freqs = out
+    elif kind == "yarn":
+        # Frequencies that turn fewer than `slow` times over the `original` positions are divided by `factor`, those
+        # that turn more than `fast` times stay, and a ramp over the pair index joins the two: the pair whose
+        # frequency turns t times is at index rotary_dim ln(original / (2 pi t)) / (2 ln theta).
+        factor, original = float(scaling["factor"]), float(scaling["original"])
+
+        def index_of(turns: float) -> float:
+            return rotary_dim * math.log(original / (2 * math.pi * turns)) / (2 * log_theta)
+
+        low = max(math.floor(index_of(float(scaling["fast"]))), 0)
+        high = min(math.ceil(index_of(float(scaling["slow"]))), rotary_dim - 1)
+        out = []
+        for i, f in enumerate(freqs):
+            ramp = min(max((i - low) / max(high - low, 0.001), 0.0), 1.0)
+            out.append(f / factor * ramp + f * (1 - ramp))
+        freqs = out
     elif kind != "default":
         raise ValueError(f"rotary scaling {kind!r} is not supported")
     return freqs
+
+
+def rotary_magnitude(scaling: Mapping | None) -> float:
+    """What the cosines and sines are multiplied by: 0.1 ln(factor) + 1 under the YaRN rule (a rotated vector grows by
+    it, and so does its share of a score), else 1."""
+    if scaling and str(scaling.get("rope_type", "default")) == "yarn":
+        return 0.1 * math.log(float(scaling["factor"])) + 1.0
+    return 1.0
 
 
 class RotaryEmbedding:
@@ -78,7 +102,8 @@ class RotaryEmbedding:
             values += [0.0] * ((self.rotary_dim - self.rotated) // 2)  # (pairs that stay as they are)
             freqs = torch.tensor(values, dtype=torch.float64)
             angles = torch.arange(rt.max_length, dtype=torch.float64)[:, None] * freqs[None, :]
-            table = torch.stack([torch.cos(angles), torch.sin(angles)], dim=-1).to(torch.float32)
+            table = (torch.stack([torch.cos(angles), torch.sin(angles)], dim=-1) * rotary_magnitude(self.scaling)) \
+                .to(torch.float32)
             return table.contiguous().to(rt.device)
 
         self._table = rt.shared(key, make)
