@@ -1,0 +1,338 @@
+// Attention with sigmoid weights mixed across heads (see sigmoid_attention.cu) for prompt-sized steps on the tensor
+// cores (bfloat16 operands, mma.sync m16n8k16, float32 accumulators).
+//
+// A block takes 16 consecutive new tokens of one sequence and ALL heads, because the mixing needs every head's weight
+// of a (query, key) pair in one place. It walks the keys the 16 tokens can see (the kept first positions, then the
+// window) in tiles of 32; per tile
+//   1. keys and values of every kv head arrive in shared memory (cp.async, two stages where they fit),
+//   2. each warp computes S_h = Q_h K^T for ITS heads and leaves w_h = sigmoid(S_h scale - slope_h (i - j) + b_h), zero
+//      where j is not visible, in shared memory as float32,
+//   3. each warp mixes, for its heads, the weights of all heads (w'_h = sum_g M[h, g] w_g) straight into the A
+//      fragments of the second product and adds w'_h V to its heads' sums.
+// The epilogue multiplies by sigmoid(gate) and rounds. Nothing is normalised over the keys, so there is no running
+// maximum and no rescaling. Warp w owns heads w * HPW .. w * HPW + HPW - 1.
+//
+// dim and vdim: multiples of 16, at most 128 (vdim) and 256 (dim). page_size: a multiple of 32.
+#include "wide_kv.cuh"
+
+namespace {
+typedef __nv_bfloat16 bf16;
+constexpr int BM = 16, BN = 32, W_LD = 40;
+
+__device__ __forceinline__ void cp_async_16(void* smem, const void* gmem) {
+  unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+__device__ __forceinline__ void ldmatrix_x4(unsigned* r, const void* p) {
+  unsigned s = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned* r, const void* p) {
+  unsigned s = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void mma_bf16(float* c, const unsigned* a, unsigned b0, unsigned b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<unsigned*>(&v);
+}
+__device__ __forceinline__ float sigmoid_fast(float s) { return 1.0f / (1.0f + __expf(-s)); }
+__device__ __forceinline__ float sigmoid_exact(float g) {
+  if (g >= 0.f) return 1.0f / (1.0f + expf(-g));
+  float e = expf(g);
+  return e / (1.0f + e);
+}
+
+struct TiledArgs {
+  const bf16* q;        // [tokens, heads * dim]
+  WideKv cache;         // bfloat16
+  const float* mix;     // [heads, heads] or null
+  const float* slopes;  // [heads] or null
+  const float* head_bias;  // [heads] or null
+  const float* gates;   // gates[token * gate_ld + o] or null
+  int gate_ld;
+  bf16* out;            // [tokens, heads * vdim]
+  int heads, window, keep, stages;
+  float scale;
+  const int* cu_seqlens;
+  const int* tok_pos;
+  const int* slots;
+};
+
+template <int HPW, int VD>
+__global__ void __launch_bounds__(256) sigmoid_tiled_kernel(TiledArgs a) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int heads = a.heads, groups = a.cache.kv_heads, share = heads / groups;
+  const int dim = a.cache.key_dim, vdim = a.cache.value_dim;
+  const int k_ld = dim + 8, v_ld = vdim + 8;
+  bf16* q_s = reinterpret_cast<bf16*>(smem_raw);                 // [heads][BM][k_ld]
+  bf16* k_s = q_s + (size_t)heads * BM * k_ld;                   // [stages][groups][BN][k_ld]
+  bf16* v_s = k_s + (size_t)a.stages * groups * BN * k_ld;       // [stages][groups][BN][v_ld]
+  float* w_s = reinterpret_cast<float*>(v_s + (size_t)a.stages * groups * BN * v_ld);  // [heads][BM][W_LD]
+  float* mix_s = w_s + (size_t)heads * BM * W_LD;                // [heads][heads]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, threads = blockDim.x;
+  pdl_launch_dependents();
+  if (a.mix != nullptr)
+    for (int i = tid; i < heads * heads; i += threads) mix_s[i] = a.mix[i];
+  pdl_wait();
+  const int b = blockIdx.y;
+  const int tok0 = a.cu_seqlens[b], n_new = a.cu_seqlens[b + 1] - tok0;
+  // (the last tokens of a sequence see the most keys: they go first)
+  const int m0 = (gridDim.x - 1 - blockIdx.x) * BM;
+  if (m0 >= n_new) return;
+  const int rows = min(BM, n_new - m0);
+  const int pos_lo = a.tok_pos[tok0] + m0, pos_hi = pos_lo + rows - 1;  // positions of new tokens are consecutive
+  const int* pages = a.cache.page_table + (size_t)a.slots[b] * a.cache.max_pages;
+
+  // the tiles this block walks: those of the kept first positions that lie before the first row's window, then from
+  // the first row's window to the last row's own position
+  const int lo = a.window > 0 ? max(0, pos_lo - a.window + 1) : 0;
+  const int kept_tiles = (min(a.keep, lo) + BN - 1) / BN;
+  const int window_first = max(lo / BN, kept_tiles);
+  const int count = kept_tiles + pos_hi / BN - window_first + 1;
+  auto first_key = [&](int index) { return (index < kept_tiles ? index : window_first + index - kept_tiles) * BN; };
+
+  const int k_pieces = dim >> 3, v_pieces = vdim >> 3;
+  auto load_tile = [&](int stage, int index) {
+    const int j0 = first_key(index);
+    const int page = pages[j0 / a.cache.page_size], row0 = j0 % a.cache.page_size;
+    const bf16* base = (const bf16*)a.cache.base;
+    bf16* kd = k_s + (size_t)stage * groups * BN * k_ld;
+    for (int idx = tid; idx < groups * BN * k_pieces; idx += threads) {
+      int g = idx / (BN * k_pieces), rest = idx - g * BN * k_pieces, r = rest / k_pieces, c = rest - r * k_pieces;
+      cp_async_16(kd + ((size_t)g * BN + r) * k_ld + c * 8, base + key_at(a.cache, page, g, row0 + r) + c * 8);
+    }
+    bf16* vd = v_s + (size_t)stage * groups * BN * v_ld;
+    for (int idx = tid; idx < groups * BN * v_pieces; idx += threads) {
+      int g = idx / (BN * v_pieces), rest = idx - g * BN * v_pieces, r = rest / v_pieces, c = rest - r * v_pieces;
+      cp_async_16(vd + ((size_t)g * BN + r) * v_ld + c * 8, base + value_at(a.cache, page, g, row0 + r) + c * 8);
+    }
+  };
+  load_tile(0, 0);
+  cp_async_commit();
+
+  // the block's queries: [head][row][dim]; rows beyond the sequence's tokens are zeros
+  for (int idx = tid; idx < heads * BM * k_pieces; idx += threads) {
+    int h = idx / (BM * k_pieces), rest = idx - h * BM * k_pieces, r = rest / k_pieces, c = rest - r * k_pieces;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < rows) v = *reinterpret_cast<const uint4*>(a.q + ((size_t)(tok0 + m0 + r) * heads + h) * dim + c * 8);
+    *reinterpret_cast<uint4*>(q_s + ((size_t)h * BM + r) * k_ld + c * 8) = v;
+  }
+
+  float o_acc[HPW][VD / 8][4];
+#pragma unroll
+  for (int e = 0; e < HPW; ++e)
+#pragma unroll
+    for (int i = 0; i < VD / 8; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) o_acc[e][i][j] = 0.f;
+  const int gq = lane >> 2, tq = lane & 3, mat = lane >> 3;
+  int row_pos[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) row_pos[i] = gq + 8 * i < rows ? pos_lo + gq + 8 * i : -1;
+  const int k_steps = dim >> 4, nv16 = vdim >> 4;
+
+  for (int index = 0; index < count; ++index) {
+    const int stage = a.stages == 2 ? (index & 1) : 0;
+    if (a.stages == 2) {
+      if (index + 1 < count) load_tile(stage ^ 1, index + 1);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();  // the tile (and, the first time, the queries) is in shared memory
+    const int j0 = first_key(index);
+    const bf16* kb = k_s + (size_t)stage * groups * BN * k_ld;
+    const bf16* vb = v_s + (size_t)stage * groups * BN * v_ld;
+    // 2. this warp's heads: scores, weights, into shared memory
+#pragma unroll
+    for (int e = 0; e < HPW; ++e) {
+      const int h = warp * HPW + e;
+      if (h >= heads) break;
+      const bf16* kg = kb + (size_t)(h / share) * BN * k_ld;
+      const bf16* qh = q_s + (size_t)h * BM * k_ld;
+      float s[BN / 8][4];
+#pragma unroll
+      for (int j = 0; j < BN / 8; ++j)
+#pragma unroll
+        for (int r = 0; r < 4; ++r) s[j][r] = 0.f;
+#pragma unroll 2
+      for (int ks = 0; ks < k_steps; ++ks) {
+        unsigned qf[4];
+        ldmatrix_x4(qf, qh + (size_t)(lane & 15) * k_ld + ks * 16 + (lane >> 4) * 8);
+#pragma unroll
+        for (int jp = 0; jp < BN / 16; ++jp) {
+          unsigned bfr[4];
+          ldmatrix_x4(bfr, kg + (size_t)(jp * 16 + (mat >> 1) * 8 + (lane & 7)) * k_ld + ks * 16 + (mat & 1) * 8);
+          mma_bf16(s[2 * jp], qf, bfr[0], bfr[1]);
+          mma_bf16(s[2 * jp + 1], qf, bfr[2], bfr[3]);
+        }
+      }
+      const float slope = a.slopes != nullptr ? a.slopes[h] : 0.f;
+      const float bias = a.head_bias != nullptr ? a.head_bias[h] : 0.f;
+      float* wh = w_s + (size_t)h * BM * W_LD;
+#pragma unroll
+      for (int j = 0; j < BN / 8; ++j)
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const int i = row_pos[half];
+          float w[2];
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            const int key = j0 + j * 8 + tq * 2 + c;
+            const bool seen = key <= i && (a.window <= 0 || i - key < a.window || key < a.keep);
+            w[c] = seen ? sigmoid_fast(fmaf(s[j][half * 2 + c], a.scale, bias - slope * (float)(i - key))) : 0.f;
+          }
+          *reinterpret_cast<float2*>(wh + (size_t)(gq + 8 * half) * W_LD + j * 8 + tq * 2) = make_float2(w[0], w[1]);
+        }
+    }
+    __syncthreads();
+    // 3. this warp's heads: mix all heads' weights into the operand, add the weighted values
+#pragma unroll
+    for (int e = 0; e < HPW; ++e) {
+      const int h = warp * HPW + e;
+      if (h >= heads) break;
+      unsigned p_frag[BN / 16][4];
+#pragma unroll
+      for (int kk = 0; kk < BN / 16; ++kk) {
+        float2 m[4];  // (row gq | gq + 8) x (columns kk * 16 + tq * 2 | + 8)
+#pragma unroll
+        for (int x = 0; x < 4; ++x) m[x] = make_float2(0.f, 0.f);
+        const int g_begin = a.mix != nullptr ? 0 : h, g_end = a.mix != nullptr ? heads : h + 1;
+        for (int g = g_begin; g < g_end; ++g) {
+          const float t = a.mix != nullptr ? mix_s[h * heads + g] : 1.0f;
+          const float* wg = w_s + (size_t)g * BM * W_LD + kk * 16 + tq * 2;
+#pragma unroll
+          for (int x = 0; x < 4; ++x) {
+            float2 w = *reinterpret_cast<const float2*>(wg + (size_t)(gq + 8 * (x & 1)) * W_LD + 8 * (x >> 1));
+            m[x].x = fmaf(t, w.x, m[x].x);
+            m[x].y = fmaf(t, w.y, m[x].y);
+          }
+        }
+#pragma unroll
+        for (int x = 0; x < 4; ++x) p_frag[kk][x] = pack_bf16(m[x].x, m[x].y);
+      }
+      const bf16* vg = vb + (size_t)(h / share) * BN * v_ld;
+#pragma unroll
+      for (int kk = 0; kk < BN / 16; ++kk) {
+#pragma unroll
+        for (int np = 0; np < VD / 16; ++np) {
+          if (np < nv16) {
+            unsigned bfr[4];
+            ldmatrix_x4_trans(bfr, vg + (size_t)(kk * 16 + (mat & 1) * 8 + (lane & 7)) * v_ld + np * 16 + (mat >> 1) * 8);
+            mma_bf16(o_acc[e][2 * np], p_frag[kk], bfr[0], bfr[1]);
+            mma_bf16(o_acc[e][2 * np + 1], p_frag[kk], bfr[2], bfr[3]);
+          }
+        }
+      }
+    }
+    __syncthreads();  // the tile's stage and the weights are free again
+    if (a.stages == 1 && index + 1 < count) {
+      load_tile(0, index + 1);
+      cp_async_commit();
+    }
+  }
+  cp_async_wait<0>();
+#pragma unroll
+  for (int e = 0; e < HPW; ++e) {
+    const int h = warp * HPW + e;
+    if (h >= heads) break;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int r = gq + 8 * half;
+      if (r >= rows) continue;
+      const size_t t = (size_t)tok0 + m0 + r;
+#pragma unroll
+      for (int i = 0; i < VD / 8; ++i) {
+        const int d = i * 8 + tq * 2;
+        if (d >= vdim) continue;
+        const size_t o = (size_t)h * vdim + d;
+        float x = o_acc[e][i][half * 2], y = o_acc[e][i][half * 2 + 1];
+        if (a.gates != nullptr) {
+          float2 z = *reinterpret_cast<const float2*>(a.gates + t * a.gate_ld + o);
+          x *= sigmoid_exact(z.x);
+          y *= sigmoid_exact(z.y);
+        }
+        *reinterpret_cast<__nv_bfloat162*>(a.out + t * heads * vdim + o) = __floats2bfloat162_rn(x, y);
+      }
+    }
+  }
+}
+
+size_t shared_bytes(int heads, int groups, int dim, int vdim, int stages) {
+  return ((size_t)heads * BM * (dim + 8) + (size_t)stages * groups * BN * (dim + 8 + vdim + 8)) * sizeof(bf16) +
+         ((size_t)heads * BM * W_LD + (size_t)heads * heads) * sizeof(float);
+}
+
+template <int HPW, int VD>
+int launch(const TiledArgs& a, int warps, size_t smem, int tiles, int n_seqs, cudaStream_t stream) {
+  static size_t configured = 0;
+  if (smem > 48 * 1024 && smem > configured) {
+    if (cudaFuncSetAttribute(sigmoid_tiled_kernel<HPW, VD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+        cudaSuccess)
+      return DLLM_LAUNCH_FAILED;
+    configured = smem;
+  }
+  return dllm_launch_pdl(sigmoid_tiled_kernel<HPW, VD>, dim3(tiles, n_seqs), dim3(warps * 32), smem, stream, a);
+}
+
+// Heads a warp owns: the fewest that give at most eight warps (a thread of these kernels takes up to 243 registers,
+// which is what 256 threads may have). 0: these sizes do not run here, because a warp's sums would not fit its
+// registers (heads x padded vdim above 256).
+int heads_per_warp(int heads, int vdim) {
+  int padded = vdim <= 64 ? 64 : 128;
+  int hpw = heads <= 8 ? 1 : (heads <= 16 ? 2 : 4);
+  if (hpw * padded > 256 || (heads + hpw - 1) / hpw > 8) return 0;
+  return hpw;
+}
+}  // namespace
+
+// 1 where the kernel below runs these sizes, else 0.
+DLLM_EXPORT int dllm_sigmoid_attention_tiled_fits(int heads, int kv_heads, int dim, int vdim, int page_size) {
+  if (heads <= 0 || kv_heads <= 0 || heads % kv_heads || dim <= 0 || dim > 256 || (dim & 15) || vdim <= 0 ||
+      vdim > 128 || (vdim & 15) || page_size <= 0 || page_size % BN)
+    return 0;
+  if (heads_per_warp(heads, vdim) == 0) return 0;
+  return shared_bytes(heads, kv_heads, dim, vdim, 1) <= 220 * 1024 ? 1 : 0;
+}
+
+// max_new: the most new tokens any sequence of the step has (the grid covers that many for every sequence; blocks
+// beyond a sequence's own tokens leave at once). gates: float32, rows of gate_ld values, 8-byte aligned.
+DLLM_EXPORT int dllm_sigmoid_attention_tiled(const void* q, void* out, const void* cache_base, const int* page_table,
+                                             int max_pages, int page_size, int heads, int kv_heads, int dim, int vdim,
+                                             const float* mix, const float* slopes, const float* head_bias,
+                                             const float* gates, int gate_ld, float scale, int window, int keep,
+                                             const int* cu_seqlens, const int* tok_pos, const int* slots, int n_seqs,
+                                             int max_new, cudaStream_t stream) {
+  if (n_seqs <= 0 || max_new <= 0) return DLLM_OK;
+  if (!dllm_sigmoid_attention_tiled_fits(heads, kv_heads, dim, vdim, page_size) || keep < 0 || n_seqs > 65535 ||
+      (gates != nullptr && ((gate_ld & 1) || ((uintptr_t)gates & 7))))
+    return DLLM_UNSUPPORTED_SIZE;
+  if (!q || !out || !cache_base || !page_table || !cu_seqlens || !tok_pos || !slots) return DLLM_BAD_ARGUMENT;
+  int stages = shared_bytes(heads, kv_heads, dim, vdim, 2) <= 110 * 1024 ? 2 : 1;
+  if (stages == 1 && shared_bytes(heads, kv_heads, dim, vdim, 2) <= 220 * 1024 &&
+      shared_bytes(heads, kv_heads, dim, vdim, 1) > 110 * 1024)
+    stages = 2;  // (one block a multiprocessor either way: the second stage costs nothing)
+  TiledArgs a{(const bf16*)q, WideKv{(void*)cache_base, page_table, max_pages, page_size, kv_heads, dim, vdim}, mix,
+              slopes, head_bias, gates, gate_ld, (bf16*)out, heads, window, keep, stages, scale, cu_seqlens, tok_pos,
+              slots};
+  size_t smem = shared_bytes(heads, kv_heads, dim, vdim, stages);
+  int hpw = heads_per_warp(heads, vdim), warps = (heads + hpw - 1) / hpw;
+  int tiles = (max_new + BM - 1) / BM;
+  bool narrow = vdim <= 64;
+  if (hpw == 1) return narrow ? launch<1, 64>(a, warps, smem, tiles, n_seqs, stream)
+                              : launch<1, 128>(a, warps, smem, tiles, n_seqs, stream);
+  if (hpw == 2) return narrow ? launch<2, 64>(a, warps, smem, tiles, n_seqs, stream)
+                              : launch<2, 128>(a, warps, smem, tiles, n_seqs, stream);
+  return launch<4, 64>(a, warps, smem, tiles, n_seqs, stream);
+}

@@ -42,6 +42,7 @@ SOURCES = {
     "latent_attention": "latent_attention.cu",
     "latent_attention_tiled": "latent_attention_tiled.cu",
     "sigmoid_attention": "sigmoid_attention.cu",
+    "sigmoid_attention_tiled": "sigmoid_attention_tiled.cu",
     "moe": "moe.cu",
     "moe_grouped": "moe_grouped.cu",
     "sampling": "sampling.cu",

@@ -44,6 +44,12 @@ _prototypes = {
                                                       c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                                       c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                                       c_int, c_int, c_void_p, c_int, c_void_p],
+    ("sigmoid_attention_tiled", "dllm_sigmoid_attention_tiled_fits"): [c_int, c_int, c_int, c_int, c_int],
+    ("sigmoid_attention_tiled", "dllm_sigmoid_attention_tiled"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                                                  c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                                                                  c_void_p, c_void_p, c_int, c_float, c_int, c_int,
+                                                                  c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                                                  c_void_p],
     ("elementwise", "dllm_norm_sum_residual"): [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float,
                                                 c_float, c_void_p],
     ("elementwise", "dllm_norm_add_residual"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p],
@@ -385,9 +391,43 @@ SIGMOID_TILES_FROM = 16
 """Steps of more tokens than this take the tensor-core form of the sigmoid attention where the sizes allow it."""
 
 
+_sigmoid_tiles: dict[tuple, bool] = {}
+
+
 def sigmoid_attention_tiles(dtype, heads: int, kv_heads: int, dim: int, vdim: int, page_size: int = 64) -> bool:
-    """Whether the tensor-core kernel runs these sizes."""
-    return False
+    """Whether the tensor-core kernel runs these sizes: bfloat16, dim and vdim multiples of 16 (vdim at most 128, dim
+    at most 256), pages of a multiple of 32 positions, a block's queries, one tile of every kv head's keys and values
+    and all heads' weights within its shared memory (the library answers, once per combination of sizes)."""
+    if dtype != torch.bfloat16 or dim % 16 or vdim % 16 or (heads * vdim) % 2:
+        return False
+    key = (heads, kv_heads, dim, vdim, page_size)
+    if key not in _sigmoid_tiles:
+        _sigmoid_tiles[key] = bool(_fn("sigmoid_attention_tiled", "dllm_sigmoid_attention_tiled_fits")(*key))
+    return _sigmoid_tiles[key]
+
+
+def sigmoid_attention_tiled(out: torch.Tensor, q: torch.Tensor, cache, heads: int, scale: float, window: int,
+                            keep: int, mix: torch.Tensor | None, slopes: torch.Tensor | None,
+                            head_bias: torch.Tensor | None, gates: torch.Tensor | None, gate_at: int, batch) -> None:
+    """`sigmoid_attention` for the new tokens of a prompt-sized step on the tensor cores: a block takes sixteen
+    consecutive tokens of a sequence and all heads, the mixed weights are rounded to bfloat16 as the operand of the
+    second product (accumulation float32). Sizes: `sigmoid_attention_tiles`."""
+    _cuda(out, q, mix, slopes, head_bias, gates)
+    dim, vdim = cache.head_dim, cache.value_dim
+    assert q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16
+    assert q.shape[1] == heads * dim and out.shape[1] == heads * vdim and not cache.keys_only
+    assert mix is None or (mix.dtype == torch.float32 and tuple(mix.shape) == (heads, heads))
+    for tensor in (slopes, head_bias):
+        assert tensor is None or (tensor.dtype == torch.float32 and tensor.numel() == heads)
+    gate_ptr = (gates.data_ptr() + 4 * int(gate_at)) if gates is not None else None
+    ptr = lambda tensor: tensor.data_ptr() if tensor is not None else None  # noqa: E731
+    _check(_fn("sigmoid_attention_tiled", "dllm_sigmoid_attention_tiled")(
+        q.data_ptr(), out.data_ptr(), cache.base_ptr, cache.page_table.data_ptr(), cache.max_pages, cache.page_size,
+        heads, cache.kv_heads, dim, vdim, ptr(mix), ptr(slopes), ptr(head_bias), gate_ptr,
+        gates.shape[1] if gates is not None else 0, float(scale), int(window), int(keep), batch.cu_seqlens.data_ptr(),
+        batch.tok_pos.data_ptr(), batch.slots.data_ptr(), batch.n_seqs, int(batch.max_new), _stream()),
+        "sigmoid_attention_tiled",
+        lambda: f"heads={heads} dim={dim} value_dim={vdim} page={cache.page_size} gate_at={gate_at}")
 
 
 def glu_clamped_fuses(rows: int, outputs: int, inner: int) -> bool:
