@@ -1012,7 +1012,75 @@ def revupel_rooflines(row: dict, size: dict, batch: int, peak: dict, contexts: l
     return out
 
 
-DESIGNS = {"tisalorn": ("Tisalorn", tisalorn_config, ("llama",)), "satavik": ("Satavik", satavik_config, ("llama",)),
+def gaperax_config(size: dict) -> dict:
+    """A Gaperax model of `size`: latent attention and windowed sigmoid attention in turn (the latent as the Revupel
+    model's: twice a head wide, at most 256, a shared rotated part of half a head, a query latent of three eighths of
+    the width, frequencies stretched four times beyond 2,048 positions), a window of 1,024 positions that keeps the
+    first 64, keys and values of a head's size, the dense gated feed-forward of the Llama model's width."""
+    h, g, d, width = size["heads"], size["kv_heads"], size["dim"], size["width"]
+    latent = {"heads": h, "dim": d, "rot_dim": d // 2, "vdim": d, "q_rank": 3 * width // 8, "kv_rank": min(2 * d, 256),
+              "scale": (d + d // 2) ** -0.5,
+              "rot": {"base": 500000.0, "dims": d // 2,
+                      "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}
+    attention = {"heads": h, "kv_heads": g, "dim": d, "vdim": d, "scale": d ** -0.5,
+                 "mask": {"size": GAPERAX_WINDOW, "keep_first": GAPERAX_KEPT}}
+    mlp = {"kind": "dense", "ff": size["ff"]}
+    layers = [{"type": "attention", "mixer": attention, "mlp": mlp} if i % 2 else
+              {"type": "latent_attention", "mixer": latent, "mlp": mlp} for i in range(size["layers"])]
+    return {"architecture": "Gaperax", "vocab": size["vocab"], "width": width, "norm": {"eps": 1e-6},
+            "max_position": 8192, "layers": layers}
+
+
+GAPERAX_WINDOW, GAPERAX_KEPT = 1024, 64
+
+
+def gaperax_rooflines(row: dict, size: dict, batch: int, peak: dict, contexts: list) -> dict:
+    """The new kernels and the kernels of the models beside that do the like work, each against its own roofline.
+    Sigmoid attention: a prompt step against the multiply-adds of the (query, key) pairs its mask lets through at the
+    bf16 tensor rate, a decode step against the keys and values a token can see at the HBM rate; beside the Llama
+    model's softmax attention (all earlier positions). Latent attention with a sink: beside the Revupel model's, the
+    same kernels. The gated feed-forward and the norm without statistics: beside the Llama model's SwiGLU and RMSNorm."""
+    h, g, d, width, ff = size["heads"], size["kv_heads"], size["dim"], size["width"], size["ff"]
+    rank, rot = min(2 * d, 256), d // 2
+    reach = GAPERAX_WINDOW + GAPERAX_KEPT
+    out = {}
+
+    def put(name, work, kernel, unit):
+        if kernel and kernel["us"]:
+            rate = work / (kernel["us"] * 1e-6)
+            out[name] = round({"hbm": rate / 1e9 / peak["hbm_gbs"], "bf16": rate / 1e12 / peak["bf16_tflops"]}[unit], 4)
+
+    pairs = sum(min(i + 1, reach) for i in range(PREFILL_TOKENS))
+    put("gaperax_attention_prefill_bf16_frac", 2 * h * 2 * d * pairs,
+        _first(row["gaperax"]["prefill_kernels"], "sigmoid_attention"), "bf16")
+    put("gaperax_attention_decode_hbm_frac", 2 * sum(min(c, reach) for c in contexts) * g * 2 * d,
+        _first(row["gaperax"]["decode_kernels"], "sigmoid_attention"), "hbm")
+    put("llama_attention_prefill_bf16_frac", 2 * h * 2 * d * PREFILL_TOKENS * PREFILL_TOKENS / 2,
+        _first(row["llama"]["prefill_kernels"], "attention"), "bf16")
+    put("llama_attention_decode_hbm_frac", 2 * sum(contexts) * g * 2 * d,
+        _first(row["llama"]["decode_kernels"], "attention"), "hbm")
+    for model in ("gaperax", "revupel"):
+        put(f"{model}_latent_prefill_bf16_frac", 2 * h * (2 * rank + rot) * PREFILL_TOKENS * PREFILL_TOKENS / 2,
+            _first(row[model]["prefill_kernels"], "latent_attention"), "bf16")
+        put(f"{model}_latent_decode_hbm_frac", 2 * sum(contexts) * (rank + rot),
+            _first(row[model]["decode_kernels"], "latent_attention"), "hbm")
+    # the feed-forward: both products (and the activation where it is a kernel of its own) of one layer
+    for model in ("gaperax", "llama"):
+        for phase, work, unit in (("decode", 2 * 3 * ff * width, "hbm"),
+                                  ("prefill", 2 * PREFILL_TOKENS * 3 * ff * width, "bf16")):
+            kernels = row[model][phase + "_kernels"]
+            us = sum(k["us"] for name, k in kernels.items()
+                     if "swiglu" in name or "glu_gelu_tanh" in name or name.startswith("glu_act")
+                     or (name.startswith("gemm") and (f"K={ff}" in name or f"N={2 * ff} " in name)))
+            put(f"{model}_feed_forward_{phase}_{unit}_frac", work, {"us": us}, unit)
+    # the norm of a prompt step: float32 rows in, bfloat16 rows out
+    for model, name in (("gaperax", "dynamic_tanh"), ("llama", "rmsnorm"), ("revupel", "rmsnorm")):
+        put(f"{model}_norm_prefill_hbm_frac", 6 * PREFILL_TOKENS * width,
+            _first(row[model]["prefill_kernels"], name), "hbm")
+    return out
+
+
+DESIGNS = {"gaperax": ("Gaperax", gaperax_config, ("revupel", "llama")), "tisalorn": ("Tisalorn", tisalorn_config, ("llama",)), "satavik": ("Satavik", satavik_config, ("llama",)),
            "revupel": ("Revupel", revupel_config, ("satavik", "tisalorn"))}
 """--design NAME: the design's name, its configuration at a size, and the models it is measured beside."""
 
@@ -1098,6 +1166,8 @@ def design_comparison(args) -> int:
             row["roofline"] = tisalorn_rooflines(row, size, args.batch, peak)
         elif design == "satavik":
             row["roofline"] = satavik_rooflines(row, size, args.batch, peak, [len(p) + 1 for p in prompts])
+        elif design == "gaperax":
+            row["roofline"] = gaperax_rooflines(row, size, args.batch, peak, [len(p) + 1 for p in prompts])
         else:
             row["roofline"] = revupel_rooflines(row, size, args.batch, peak, [len(p) + 1 for p in prompts])
         for other in beside:
