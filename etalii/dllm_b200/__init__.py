@@ -1,4 +1,4 @@
-"""A small generation library for one B200 (Llama, Tisalorn, Satavik and Revupel architectures): typed configuration and a registry, weights by name, layers put
+"""A small generation library for one B200 (Llama, Tisalorn, Satavik, Revupel and Gaperax architectures): typed configuration and a registry, weights by name, layers put
 together from parts, a paged cache with slots, one step function, a generation loop, sampling, and hand-written
 sm_100a kernels underneath."""
 from .config.registry import ConfigError, config_from_dict, load_config, register_architecture  # noqa: F401

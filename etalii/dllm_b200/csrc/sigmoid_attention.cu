@@ -309,6 +309,29 @@ DLLM_EXPORT int dllm_sigmoid_prepare(const float* rows, int stride, int q_at, in
   return DLLM_BAD_ARGUMENT;
 }
 
+// out[t, o] = (sum over splits of part[split][t][o]) * sigmoid(gates[t * gate_ld + o]), rounded to `dtype`: the second
+// step of an attention kernel that dealt the keys to several blocks (this library's, or the tile kernel's).
+DLLM_EXPORT int dllm_sigmoid_combine(const float* part, const float* gates, int gate_ld, void* out, int tokens,
+                                     int outputs, int splits, int dtype, cudaStream_t stream) {
+  if (tokens <= 0) return DLLM_OK;
+  if (outputs <= 0 || splits < 1) return DLLM_UNSUPPORTED_SIZE;
+  if (!part || !out) return DLLM_BAD_ARGUMENT;
+  SigmoidArgs a{};
+  a.part = const_cast<float*>(part);
+  a.gates = gates;
+  a.gate_ld = gate_ld;
+  a.out = out;
+  a.tokens = tokens;
+  a.splits = splits;
+  int across = (outputs + 255) / 256;
+  dim3 grid(tokens, across > 16 ? 16 : across);
+  if (dtype == DLLM_F32)
+    return dllm_launch_pdl(sigmoid_combine_kernel<float>, grid, dim3(256), 0, stream, a, outputs);
+  if (dtype == DLLM_BF16)
+    return dllm_launch_pdl(sigmoid_combine_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, a, outputs);
+  return DLLM_BAD_ARGUMENT;
+}
+
 // window <= 0: every earlier position is seen. splits > 1: `part` holds splits x tokens x heads x vdim floats.
 DLLM_EXPORT int dllm_sigmoid_attention(const void* q, void* out, void* cache_base, const int* page_table,
                                        int max_pages, int page_size, int heads, int kv_heads, int dim, int vdim,

@@ -6,11 +6,15 @@
 // window) in tiles of 32; per tile
 //   1. keys and values of every kv head arrive in shared memory (cp.async, two stages where they fit),
 //   2. each warp computes S_h = Q_h K^T for ITS heads and leaves w_h = sigmoid(S_h scale - slope_h (i - j) + b_h), zero
-//      where j is not visible, in shared memory as float32,
-//   3. each warp mixes, for its heads, the weights of all heads (w'_h = sum_g M[h, g] w_g) straight into the A
-//      fragments of the second product and adds w'_h V to its heads' sums.
-// The epilogue multiplies by sigmoid(gate) and rounds. Nothing is normalised over the keys, so there is no running
-// maximum and no rescaling. Warp w owns heads w * HPW .. w * HPW + HPW - 1.
+//      where j is not visible, in shared memory as bfloat16 [head][query][key],
+//   3. the mixing w'_h = sum_g M[h, g] w_g is itself a product on the tensor cores: M (bfloat16 fragments that every
+//      warp holds in registers for the whole kernel) times the [head] x [query, key] matrix of weights, each warp a
+//      stretch of the tile's (query, key) pairs; the mixed weights go back to shared memory as bfloat16,
+//   4. each warp adds w'_h V for its heads to their sums.
+// Without a mixing matrix step 3 is left out. The epilogue multiplies by sigmoid(gate) and rounds. Nothing is
+// normalised over the keys, so there is no running maximum and no rescaling. Warp w owns heads w * HPW .. w * HPW +
+// HPW - 1. (With the mixing as float32 multiply-adds out of shared memory, a head's 16 x 32 weights from all heads'
+// at 8 multiply-adds per load, a warp spent 1,000 of its 2,500 instructions a tile there and 800 on exact sigmoids.)
 //
 // dim and vdim: multiples of 16, at most 128 (vdim) and 256 (dim). page_size: a multiple of 32.
 #include "wide_kv.cuh"
@@ -18,6 +22,8 @@
 namespace {
 typedef __nv_bfloat16 bf16;
 constexpr int BM = 16, BN = 32, W_LD = 40;
+constexpr int W_PLANE = BM * W_LD + 8;  // a head's weights; the 8 keep ldmatrix over eight heads off one bank
+constexpr int MAX_HEAD_TILES = 2;       // the mixing matrix in registers: up to 32 heads
 
 __device__ __forceinline__ void cp_async_16(void* smem, const void* gmem) {
   unsigned s = (unsigned)__cvta_generic_to_shared(smem);
@@ -41,11 +47,17 @@ __device__ __forceinline__ void mma_bf16(float* c, const unsigned* a, unsigned b
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+constexpr float LOG2E = 1.4426950408889634f;
 __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<unsigned*>(&v);
 }
-__device__ __forceinline__ float sigmoid_fast(float s) { return 1.0f / (1.0f + __expf(-s)); }
+// 1 / (1 + 2^x) with the hardware's approximations (x = -score * log2 e; 2^x = inf gives 0).
+__device__ __forceinline__ float sigmoid_of_exp2(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(1.0f + fast_exp2(x)));
+  return y;
+}
 __device__ __forceinline__ float sigmoid_exact(float g) {
   if (g >= 0.f) return 1.0f / (1.0f + expf(-g));
   float e = expf(g);
@@ -61,6 +73,8 @@ struct TiledArgs {
   const float* gates;   // gates[token * gate_ld + o] or null
   int gate_ld;
   bf16* out;            // [tokens, heads * vdim]
+  float* part;          // splits > 1: [split][token][heads * vdim] float32 sums, no gate (sigmoid_combine finishes)
+  int splits, tokens;   // blocks that share a block's tiles of keys (blockIdx.z); the step's tokens
   int heads, window, keep, stages;
   float scale;
   const int* cu_seqlens;
@@ -77,12 +91,30 @@ __global__ void __launch_bounds__(256) sigmoid_tiled_kernel(TiledArgs a) {
   bf16* q_s = reinterpret_cast<bf16*>(smem_raw);                 // [heads][BM][k_ld]
   bf16* k_s = q_s + (size_t)heads * BM * k_ld;                   // [stages][groups][BN][k_ld]
   bf16* v_s = k_s + (size_t)a.stages * groups * BN * k_ld;       // [stages][groups][BN][v_ld]
-  float* w_s = reinterpret_cast<float*>(v_s + (size_t)a.stages * groups * BN * v_ld);  // [heads][BM][W_LD]
-  float* mix_s = w_s + (size_t)heads * BM * W_LD;                // [heads][heads]
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, threads = blockDim.x;
+  const int head_tiles = (heads + 15) >> 4;
+  bf16* w_s = v_s + (size_t)a.stages * groups * BN * v_ld;       // [16 head_tiles][W_PLANE]: weights before the mixing
+  bf16* p_s = a.mix != nullptr ? w_s + (size_t)head_tiles * 16 * W_PLANE : w_s;  // ... and after it (or the same)
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, threads = blockDim.x, warps = threads >> 5;
+  const int gq = lane >> 2, tq = lane & 3, mat = lane >> 3;
   pdl_launch_dependents();
-  if (a.mix != nullptr)
-    for (int i = tid; i < heads * heads; i += threads) mix_s[i] = a.mix[i];
+  // the mixing matrix as the left operand's fragments: tile (mt, kt) holds M[16 mt + row][16 kt + column]
+  unsigned m_frag[MAX_HEAD_TILES][MAX_HEAD_TILES][4];
+  if (a.mix != nullptr) {
+#pragma unroll
+    for (int mt = 0; mt < MAX_HEAD_TILES; ++mt)
+#pragma unroll
+      for (int kt = 0; kt < MAX_HEAD_TILES; ++kt)
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+          int h = mt * 16 + gq + 8 * (x & 1), g = kt * 16 + tq * 2 + 8 * (x >> 1);
+          float lo = h < heads && g < heads ? a.mix[h * heads + g] : 0.f;
+          float hi = h < heads && g + 1 < heads ? a.mix[h * heads + g + 1] : 0.f;
+          m_frag[mt][kt][x] = pack_bf16(lo, hi);
+        }
+    // heads beyond the model's (the padding of the last tile of 16) have weights of zero for good
+    for (int i = tid; i < (head_tiles * 16 - heads) * W_PLANE; i += threads)
+      w_s[(size_t)heads * W_PLANE + i] = __float2bfloat16_rn(0.f);
+  }
   pdl_wait();
   const int b = blockIdx.y;
   const int tok0 = a.cu_seqlens[b], n_new = a.cu_seqlens[b + 1] - tok0;
@@ -101,6 +133,18 @@ __global__ void __launch_bounds__(256) sigmoid_tiled_kernel(TiledArgs a) {
   const int count = kept_tiles + pos_hi / BN - window_first + 1;
   auto first_key = [&](int index) { return (index < kept_tiles ? index : window_first + index - kept_tiles) * BN; };
 
+  int begin = 0, end = count;
+  if (a.splits > 1) {
+    const int per = (count + a.splits - 1) / a.splits;
+    begin = blockIdx.z * per;
+    end = min(count, begin + per);
+    if (begin >= end) {  // nothing left for this block: its rows' sums are zeros
+      const int outputs = heads * vdim;
+      for (int i = tid; i < rows * outputs; i += threads)
+        a.part[((size_t)blockIdx.z * a.tokens + tok0 + m0 + i / outputs) * outputs + i % outputs] = 0.f;
+      return;
+    }
+  }
   const int k_pieces = dim >> 3, v_pieces = vdim >> 3;
   auto load_tile = [&](int stage, int index) {
     const int j0 = first_key(index);
@@ -117,7 +161,7 @@ __global__ void __launch_bounds__(256) sigmoid_tiled_kernel(TiledArgs a) {
       cp_async_16(vd + ((size_t)g * BN + r) * v_ld + c * 8, base + value_at(a.cache, page, g, row0 + r) + c * 8);
     }
   };
-  load_tile(0, 0);
+  load_tile(0, begin);
   cp_async_commit();
 
   // the block's queries: [head][row][dim]; rows beyond the sequence's tokens are zeros
@@ -135,16 +179,15 @@ __global__ void __launch_bounds__(256) sigmoid_tiled_kernel(TiledArgs a) {
     for (int i = 0; i < VD / 8; ++i)
 #pragma unroll
       for (int j = 0; j < 4; ++j) o_acc[e][i][j] = 0.f;
-  const int gq = lane >> 2, tq = lane & 3, mat = lane >> 3;
   int row_pos[2];
 #pragma unroll
   for (int i = 0; i < 2; ++i) row_pos[i] = gq + 8 * i < rows ? pos_lo + gq + 8 * i : -1;
   const int k_steps = dim >> 4, nv16 = vdim >> 4;
 
-  for (int index = 0; index < count; ++index) {
-    const int stage = a.stages == 2 ? (index & 1) : 0;
+  for (int index = begin; index < end; ++index) {
+    const int stage = a.stages == 2 ? ((index - begin) & 1) : 0;
     if (a.stages == 2) {
-      if (index + 1 < count) load_tile(stage ^ 1, index + 1);
+      if (index + 1 < end) load_tile(stage ^ 1, index + 1);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
@@ -178,66 +221,100 @@ __global__ void __launch_bounds__(256) sigmoid_tiled_kernel(TiledArgs a) {
           mma_bf16(s[2 * jp + 1], qf, bfr[2], bfr[3]);
         }
       }
-      const float slope = a.slopes != nullptr ? a.slopes[h] : 0.f;
-      const float bias = a.head_bias != nullptr ? a.head_bias[h] : 0.f;
-      float* wh = w_s + (size_t)h * BM * W_LD;
+      // -(score) in units of log2 e: x = S * (-scale log2 e) + c_row + slope' * (column), with the row's constant
+      // c_row = (slope (i - j0) - bias) log2 e and slope' = -slope log2 e
+      const float slope = a.slopes != nullptr ? a.slopes[h] * LOG2E : 0.f;
+      const float bias = a.head_bias != nullptr ? a.head_bias[h] * LOG2E : 0.f;
+      const float scale = -a.scale * LOG2E;
+      bf16* wh = w_s + (size_t)h * W_PLANE;
+      // a tile all of whose keys every row sees needs no mask
+      const bool open = j0 + BN - 1 <= pos_lo && rows == BM &&
+                        (a.window <= 0 || pos_hi - j0 < a.window || j0 + BN <= a.keep);
 #pragma unroll
-      for (int j = 0; j < BN / 8; ++j)
+      for (int half = 0; half < 2; ++half) {
+        const int i = row_pos[half];
+        const float c_row = fmaf(slope, (float)(i - j0 - tq * 2), -bias);
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          const int i = row_pos[half];
+        for (int j = 0; j < BN / 8; ++j) {
           float w[2];
 #pragma unroll
           for (int c = 0; c < 2; ++c) {
-            const int key = j0 + j * 8 + tq * 2 + c;
-            const bool seen = key <= i && (a.window <= 0 || i - key < a.window || key < a.keep);
-            w[c] = seen ? sigmoid_fast(fmaf(s[j][half * 2 + c], a.scale, bias - slope * (float)(i - key))) : 0.f;
+            w[c] = sigmoid_of_exp2(fmaf(s[j][half * 2 + c], scale, fmaf(-slope, (float)(j * 8 + c), c_row)));
+            if (!open) {
+              const int key = j0 + j * 8 + tq * 2 + c;
+              if (!(key <= i && (a.window <= 0 || i - key < a.window || key < a.keep))) w[c] = 0.f;
+            }
           }
-          *reinterpret_cast<float2*>(wh + (size_t)(gq + 8 * half) * W_LD + j * 8 + tq * 2) = make_float2(w[0], w[1]);
+          *reinterpret_cast<unsigned*>(wh + (size_t)(gq + 8 * half) * W_LD + j * 8 + tq * 2) = pack_bf16(w[0], w[1]);
         }
+      }
     }
     __syncthreads();
-    // 3. this warp's heads: mix all heads' weights into the operand, add the weighted values
+    // 3. the mixing as a product: P[h][pair] = sum_g M[h][g] W[g][pair], pairs = the tile's (query, key) places; a warp
+    // takes every warps-th stretch of 16 keys of a query row
+    if (a.mix != nullptr) {
+      for (int item = warp; item < BM * (BN / 16); item += warps) {
+        const int row = item / (BN / 16), col = (item - row * (BN / 16)) * 16;
+        float d[MAX_HEAD_TILES][2][4];
+#pragma unroll
+        for (int mt = 0; mt < MAX_HEAD_TILES; ++mt)
+#pragma unroll
+          for (int n = 0; n < 2; ++n)
+#pragma unroll
+            for (int x = 0; x < 4; ++x) d[mt][n][x] = 0.f;
+#pragma unroll
+        for (int kt = 0; kt < MAX_HEAD_TILES; ++kt) {
+          if (kt < head_tiles) {
+            unsigned bfr[4];  // heads 16 kt + (0..7 | 8..15) x keys col + (0..7 | 8..15)
+            ldmatrix_x4_trans(bfr, w_s + (size_t)(kt * 16 + (mat & 1) * 8 + (lane & 7)) * W_PLANE + row * W_LD + col +
+                                       (mat >> 1) * 8);
+#pragma unroll
+            for (int mt = 0; mt < MAX_HEAD_TILES; ++mt) {
+              if (mt < head_tiles) {
+                mma_bf16(d[mt][0], m_frag[mt][kt], bfr[0], bfr[1]);
+                mma_bf16(d[mt][1], m_frag[mt][kt], bfr[2], bfr[3]);
+              }
+            }
+          }
+        }
+#pragma unroll
+        for (int mt = 0; mt < MAX_HEAD_TILES; ++mt)
+#pragma unroll
+          for (int n = 0; n < 2; ++n)
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+              const int h = mt * 16 + gq + 8 * half;
+              if (mt < head_tiles && h < heads)
+                *reinterpret_cast<unsigned*>(p_s + (size_t)h * W_PLANE + row * W_LD + col + n * 8 + tq * 2) =
+                    pack_bf16(d[mt][n][half * 2], d[mt][n][half * 2 + 1]);
+            }
+      }
+      __syncthreads();
+    }
+    // 4. this warp's heads: add the weighted values
 #pragma unroll
     for (int e = 0; e < HPW; ++e) {
       const int h = warp * HPW + e;
       if (h >= heads) break;
-      unsigned p_frag[BN / 16][4];
-#pragma unroll
-      for (int kk = 0; kk < BN / 16; ++kk) {
-        float2 m[4];  // (row gq | gq + 8) x (columns kk * 16 + tq * 2 | + 8)
-#pragma unroll
-        for (int x = 0; x < 4; ++x) m[x] = make_float2(0.f, 0.f);
-        const int g_begin = a.mix != nullptr ? 0 : h, g_end = a.mix != nullptr ? heads : h + 1;
-        for (int g = g_begin; g < g_end; ++g) {
-          const float t = a.mix != nullptr ? mix_s[h * heads + g] : 1.0f;
-          const float* wg = w_s + (size_t)g * BM * W_LD + kk * 16 + tq * 2;
-#pragma unroll
-          for (int x = 0; x < 4; ++x) {
-            float2 w = *reinterpret_cast<const float2*>(wg + (size_t)(gq + 8 * (x & 1)) * W_LD + 8 * (x >> 1));
-            m[x].x = fmaf(t, w.x, m[x].x);
-            m[x].y = fmaf(t, w.y, m[x].y);
-          }
-        }
-#pragma unroll
-        for (int x = 0; x < 4; ++x) p_frag[kk][x] = pack_bf16(m[x].x, m[x].y);
-      }
+      const bf16* ph = p_s + (size_t)h * W_PLANE;
       const bf16* vg = vb + (size_t)(h / share) * BN * v_ld;
 #pragma unroll
       for (int kk = 0; kk < BN / 16; ++kk) {
+        unsigned p_frag[4];
+        ldmatrix_x4(p_frag, ph + (size_t)(lane & 15) * W_LD + kk * 16 + (lane >> 4) * 8);
 #pragma unroll
         for (int np = 0; np < VD / 16; ++np) {
           if (np < nv16) {
             unsigned bfr[4];
             ldmatrix_x4_trans(bfr, vg + (size_t)(kk * 16 + (mat & 1) * 8 + (lane & 7)) * v_ld + np * 16 + (mat >> 1) * 8);
-            mma_bf16(o_acc[e][2 * np], p_frag[kk], bfr[0], bfr[1]);
-            mma_bf16(o_acc[e][2 * np + 1], p_frag[kk], bfr[2], bfr[3]);
+            mma_bf16(o_acc[e][2 * np], p_frag, bfr[0], bfr[1]);
+            mma_bf16(o_acc[e][2 * np + 1], p_frag, bfr[2], bfr[3]);
           }
         }
       }
     }
     __syncthreads();  // the tile's stage and the weights are free again
-    if (a.stages == 1 && index + 1 < count) {
+    if (a.stages == 1 && index + 1 < end) {
       load_tile(0, index + 1);
       cp_async_commit();
     }
@@ -258,6 +335,10 @@ __global__ void __launch_bounds__(256) sigmoid_tiled_kernel(TiledArgs a) {
         if (d >= vdim) continue;
         const size_t o = (size_t)h * vdim + d;
         float x = o_acc[e][i][half * 2], y = o_acc[e][i][half * 2 + 1];
+        if (a.splits > 1) {
+          *reinterpret_cast<float2*>(a.part + ((size_t)blockIdx.z * a.tokens + t) * heads * vdim + o) = make_float2(x, y);
+          continue;
+        }
         if (a.gates != nullptr) {
           float2 z = *reinterpret_cast<const float2*>(a.gates + t * a.gate_ld + o);
           x *= sigmoid_exact(z.x);
@@ -269,9 +350,10 @@ __global__ void __launch_bounds__(256) sigmoid_tiled_kernel(TiledArgs a) {
   }
 }
 
-size_t shared_bytes(int heads, int groups, int dim, int vdim, int stages) {
-  return ((size_t)heads * BM * (dim + 8) + (size_t)stages * groups * BN * (dim + 8 + vdim + 8)) * sizeof(bf16) +
-         ((size_t)heads * BM * W_LD + (size_t)heads * heads) * sizeof(float);
+size_t shared_bytes(int heads, int groups, int dim, int vdim, int stages, bool mixes = true) {
+  size_t planes = (size_t)((heads + 15) / 16) * 16 * (mixes ? 2 : 1);
+  return ((size_t)heads * BM * (dim + 8) + (size_t)stages * groups * BN * (dim + 8 + vdim + 8) + planes * W_PLANE) *
+         sizeof(bf16);
 }
 
 template <int HPW, int VD>
@@ -283,7 +365,8 @@ int launch(const TiledArgs& a, int warps, size_t smem, int tiles, int n_seqs, cu
       return DLLM_LAUNCH_FAILED;
     configured = smem;
   }
-  return dllm_launch_pdl(sigmoid_tiled_kernel<HPW, VD>, dim3(tiles, n_seqs), dim3(warps * 32), smem, stream, a);
+  return dllm_launch_pdl(sigmoid_tiled_kernel<HPW, VD>, dim3(tiles, n_seqs, a.splits), dim3(warps * 32), smem, stream,
+                         a);
 }
 
 // Heads a warp owns: the fewest that give at most eight warps (a thread of these kernels takes up to 243 registers,
@@ -302,30 +385,34 @@ DLLM_EXPORT int dllm_sigmoid_attention_tiled_fits(int heads, int kv_heads, int d
   if (heads <= 0 || kv_heads <= 0 || heads % kv_heads || dim <= 0 || dim > 256 || (dim & 15) || vdim <= 0 ||
       vdim > 128 || (vdim & 15) || page_size <= 0 || page_size % BN)
     return 0;
-  if (heads_per_warp(heads, vdim) == 0) return 0;
+  if (heads_per_warp(heads, vdim) == 0 || heads > 16 * MAX_HEAD_TILES) return 0;
   return shared_bytes(heads, kv_heads, dim, vdim, 1) <= 220 * 1024 ? 1 : 0;
 }
 
 // max_new: the most new tokens any sequence of the step has (the grid covers that many for every sequence; blocks
-// beyond a sequence's own tokens leave at once). gates: float32, rows of gate_ld values, 8-byte aligned.
+// beyond a sequence's own tokens leave at once). gates: float32, rows of gate_ld values, 8-byte aligned. splits > 1:
+// the tiles of keys a block of 16 tokens walks are dealt to that many blocks, which leave float32 sums in `part`
+// [splits][tokens][heads x vdim] for `dllm_sigmoid_combine` (sigmoid_attention.cu) to add, gate and round; `out` and
+// `gates` are then not used here.
 DLLM_EXPORT int dllm_sigmoid_attention_tiled(const void* q, void* out, const void* cache_base, const int* page_table,
                                              int max_pages, int page_size, int heads, int kv_heads, int dim, int vdim,
                                              const float* mix, const float* slopes, const float* head_bias,
                                              const float* gates, int gate_ld, float scale, int window, int keep,
                                              const int* cu_seqlens, const int* tok_pos, const int* slots, int n_seqs,
-                                             int max_new, cudaStream_t stream) {
+                                             int max_new, int splits, float* part, int tokens, cudaStream_t stream) {
   if (n_seqs <= 0 || max_new <= 0) return DLLM_OK;
   if (!dllm_sigmoid_attention_tiled_fits(heads, kv_heads, dim, vdim, page_size) || keep < 0 || n_seqs > 65535 ||
       (gates != nullptr && ((gate_ld & 1) || ((uintptr_t)gates & 7))))
     return DLLM_UNSUPPORTED_SIZE;
   if (!q || !out || !cache_base || !page_table || !cu_seqlens || !tok_pos || !slots) return DLLM_BAD_ARGUMENT;
+  if (splits < 1 || splits > 65535 || (splits > 1 && (!part || tokens <= 0))) return DLLM_BAD_ARGUMENT;
   int stages = shared_bytes(heads, kv_heads, dim, vdim, 2) <= 110 * 1024 ? 2 : 1;
   if (stages == 1 && shared_bytes(heads, kv_heads, dim, vdim, 2) <= 220 * 1024 &&
       shared_bytes(heads, kv_heads, dim, vdim, 1) > 110 * 1024)
     stages = 2;  // (one block a multiprocessor either way: the second stage costs nothing)
   TiledArgs a{(const bf16*)q, WideKv{(void*)cache_base, page_table, max_pages, page_size, kv_heads, dim, vdim}, mix,
-              slopes, head_bias, gates, gate_ld, (bf16*)out, heads, window, keep, stages, scale, cu_seqlens, tok_pos,
-              slots};
+              slopes, head_bias, gates, gate_ld, (bf16*)out, part, splits, tokens, heads, window, keep, stages, scale,
+              cu_seqlens, tok_pos, slots};
   size_t smem = shared_bytes(heads, kv_heads, dim, vdim, stages);
   int hpw = heads_per_warp(heads, vdim), warps = (heads + hpw - 1) / hpw;
   int tiles = (max_new + BM - 1) / BM;

@@ -49,7 +49,9 @@ _prototypes = {
                                                                   c_int, c_int, c_int, c_int, c_void_p, c_void_p,
                                                                   c_void_p, c_void_p, c_int, c_float, c_int, c_int,
                                                                   c_void_p, c_void_p, c_void_p, c_int, c_int,
-                                                                  c_void_p],
+                                                                  c_int, c_void_p, c_int, c_void_p],
+    ("sigmoid_attention", "dllm_sigmoid_combine"): [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
+                                                    c_void_p],
     ("elementwise", "dllm_norm_sum_residual"): [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float,
                                                 c_float, c_void_p],
     ("elementwise", "dllm_norm_add_residual"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p],
@@ -387,10 +389,6 @@ def sigmoid_attention(out: torch.Tensor, q: torch.Tensor, cache, heads: int, sca
         "sigmoid_attention", lambda: f"heads={heads} dim={dim} value_dim={vdim} page={cache.page_size}")
 
 
-SIGMOID_TILES_FROM = 16
-"""Steps of more tokens than this take the tensor-core form of the sigmoid attention where the sizes allow it."""
-
-
 _sigmoid_tiles: dict[tuple, bool] = {}
 
 
@@ -406,12 +404,26 @@ def sigmoid_attention_tiles(dtype, heads: int, kv_heads: int, dim: int, vdim: in
     return _sigmoid_tiles[key]
 
 
+def sigmoid_tiled_splits(batch, window: int, keep: int) -> int:
+    """Over how many blocks the tile kernel deals the keys of a block of sixteen tokens: one where the step's blocks
+    cover half the multiprocessors by themselves, else enough for about two blocks each, every block with two tiles
+    of 32 keys or more."""
+    blocks = batch.n_seqs * (-(-batch.max_new // 16))
+    if blocks >= 74:
+        return 1
+    reach = batch.max_context if window <= 0 else min(batch.max_context, window + keep + 32)
+    return max(1, min(296 // blocks, reach // 64))
+
+
 def sigmoid_attention_tiled(out: torch.Tensor, q: torch.Tensor, cache, heads: int, scale: float, window: int,
                             keep: int, mix: torch.Tensor | None, slopes: torch.Tensor | None,
-                            head_bias: torch.Tensor | None, gates: torch.Tensor | None, gate_at: int, batch) -> None:
-    """`sigmoid_attention` for the new tokens of a prompt-sized step on the tensor cores: a block takes sixteen
-    consecutive tokens of a sequence and all heads, the mixed weights are rounded to bfloat16 as the operand of the
-    second product (accumulation float32). Sizes: `sigmoid_attention_tiles`."""
+                            head_bias: torch.Tensor | None, gates: torch.Tensor | None, gate_at: int, batch,
+                            ws=None) -> None:
+    """`sigmoid_attention` on the tensor cores: a block takes sixteen consecutive new tokens of a sequence and all
+    heads; the weights are rounded to bfloat16 before the mixing (itself a tensor-core product) and after it, as the
+    operand of the product with the values (accumulation float32). With `ws`, a step of few blocks (single tokens)
+    deals each block's keys to several blocks and a second kernel adds their float32 sums. Sizes:
+    `sigmoid_attention_tiles`."""
     _cuda(out, q, mix, slopes, head_bias, gates)
     dim, vdim = cache.head_dim, cache.value_dim
     assert q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16
@@ -420,14 +432,22 @@ def sigmoid_attention_tiled(out: torch.Tensor, q: torch.Tensor, cache, heads: in
     for tensor in (slopes, head_bias):
         assert tensor is None or (tensor.dtype == torch.float32 and tensor.numel() == heads)
     gate_ptr = (gates.data_ptr() + 4 * int(gate_at)) if gates is not None else None
+    gate_ld = gates.shape[1] if gates is not None else 0
     ptr = lambda tensor: tensor.data_ptr() if tensor is not None else None  # noqa: E731
+    tokens = batch.n_tokens
+    splits = sigmoid_tiled_splits(batch, window, keep) if ws is not None else 1
+    part = ws.buffer("sigmoid_part", (splits * tokens * heads * vdim,), torch.float32) if splits > 1 else None
     _check(_fn("sigmoid_attention_tiled", "dllm_sigmoid_attention_tiled")(
         q.data_ptr(), out.data_ptr(), cache.base_ptr, cache.page_table.data_ptr(), cache.max_pages, cache.page_size,
-        heads, cache.kv_heads, dim, vdim, ptr(mix), ptr(slopes), ptr(head_bias), gate_ptr,
-        gates.shape[1] if gates is not None else 0, float(scale), int(window), int(keep), batch.cu_seqlens.data_ptr(),
-        batch.tok_pos.data_ptr(), batch.slots.data_ptr(), batch.n_seqs, int(batch.max_new), _stream()),
+        heads, cache.kv_heads, dim, vdim, ptr(mix), ptr(slopes), ptr(head_bias), gate_ptr, gate_ld, float(scale),
+        int(window), int(keep), batch.cu_seqlens.data_ptr(), batch.tok_pos.data_ptr(), batch.slots.data_ptr(),
+        batch.n_seqs, int(batch.max_new), splits, ptr(part), tokens, _stream()),
         "sigmoid_attention_tiled",
         lambda: f"heads={heads} dim={dim} value_dim={vdim} page={cache.page_size} gate_at={gate_at}")
+    if splits > 1:
+        _check(_fn("sigmoid_attention", "dllm_sigmoid_combine")(
+            part.data_ptr(), gate_ptr, gate_ld, out.data_ptr(), tokens, heads * vdim, splits, _code(out.dtype),
+            _stream()), "sigmoid_combine")
 
 
 def glu_clamped_fuses(rows: int, outputs: int, inner: int) -> bool:

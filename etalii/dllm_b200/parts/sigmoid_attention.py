@@ -102,10 +102,9 @@ class SigmoidAttention:
                             write_cache)
         attended = rt.ws.buffer("attended", (n, heads * vdim), rt.dtype)
         gates, gate_at = (rows, v_at + groups * vdim) if self.gate else (None, 0)
-        if ops.sigmoid_attention_tiles(rt.dtype, heads, groups, dim, vdim, cache.page_size) and \
-                n > ops.SIGMOID_TILES_FROM:
+        if ops.sigmoid_attention_tiles(rt.dtype, heads, groups, dim, vdim, cache.page_size):
             ops.sigmoid_attention_tiled(attended, q, cache, heads, self.scale, self.window, self.keep_first, self.mix,
-                                        self.slopes, self.head_biases, gates, gate_at, batch)
+                                        self.slopes, self.head_biases, gates, gate_at, batch, rt.ws)
         else:
             ops.sigmoid_attention(attended, q, cache, heads, self.scale, self.window, self.keep_first, self.mix,
                                   self.slopes, self.head_biases, gates, gate_at, batch, rt.ws)
