@@ -83,7 +83,7 @@ struct TiledArgs {
 };
 
 template <int HPW, int VD>
-__global__ void __launch_bounds__(256) sigmoid_tiled_kernel(TiledArgs a) {
+__global__ void __launch_bounds__(HPW == 1 && VD == 64 ? 512 : 256) sigmoid_tiled_kernel(TiledArgs a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int heads = a.heads, groups = a.cache.kv_heads, share = heads / groups;
   const int dim = a.cache.key_dim, vdim = a.cache.value_dim;
@@ -145,21 +145,28 @@ __global__ void __launch_bounds__(256) sigmoid_tiled_kernel(TiledArgs a) {
       return;
     }
   }
+  // A row of keys (or values) of one kv head is copied by a power-of-two stretch of a warp's lanes, 16 bytes a lane, so
+  // that finding a lane's row and piece takes shifts only.
   const int k_pieces = dim >> 3, v_pieces = vdim >> 3;
+  int k_shift = 0, v_shift = 0;
+  while ((1 << k_shift) < k_pieces) ++k_shift;
+  while ((1 << v_shift) < v_pieces) ++v_shift;
+  auto load_rows = [&](bf16* dst, int ld, int pieces, int shift, int width, size_t first, size_t per_group) {
+    const int piece = lane & ((1 << shift) - 1), rows_at_once = 32 >> shift;
+    if (piece >= pieces) return;
+    const bf16* base = (const bf16*)a.cache.base + first + piece * 8;
+    for (int rr = warp * rows_at_once + (lane >> shift); rr < groups * BN; rr += warps * rows_at_once) {
+      const int g = rr / BN, r = rr % BN;  // (BN is a power of two)
+      cp_async_16(dst + (size_t)rr * ld + piece * 8, base + g * per_group + (size_t)r * width);
+    }
+  };
   auto load_tile = [&](int stage, int index) {
     const int j0 = first_key(index);
     const int page = pages[j0 / a.cache.page_size], row0 = j0 % a.cache.page_size;
-    const bf16* base = (const bf16*)a.cache.base;
-    bf16* kd = k_s + (size_t)stage * groups * BN * k_ld;
-    for (int idx = tid; idx < groups * BN * k_pieces; idx += threads) {
-      int g = idx / (BN * k_pieces), rest = idx - g * BN * k_pieces, r = rest / k_pieces, c = rest - r * k_pieces;
-      cp_async_16(kd + ((size_t)g * BN + r) * k_ld + c * 8, base + key_at(a.cache, page, g, row0 + r) + c * 8);
-    }
-    bf16* vd = v_s + (size_t)stage * groups * BN * v_ld;
-    for (int idx = tid; idx < groups * BN * v_pieces; idx += threads) {
-      int g = idx / (BN * v_pieces), rest = idx - g * BN * v_pieces, r = rest / v_pieces, c = rest - r * v_pieces;
-      cp_async_16(vd + ((size_t)g * BN + r) * v_ld + c * 8, base + value_at(a.cache, page, g, row0 + r) + c * 8);
-    }
+    load_rows(k_s + (size_t)stage * groups * BN * k_ld, k_ld, k_pieces, k_shift, dim, key_at(a.cache, page, 0, row0),
+              (size_t)a.cache.page_size * dim);
+    load_rows(v_s + (size_t)stage * groups * BN * v_ld, v_ld, v_pieces, v_shift, vdim,
+              value_at(a.cache, page, 0, row0), (size_t)a.cache.page_size * vdim);
   };
   load_tile(0, begin);
   cp_async_commit();
@@ -183,6 +190,15 @@ __global__ void __launch_bounds__(256) sigmoid_tiled_kernel(TiledArgs a) {
 #pragma unroll
   for (int i = 0; i < 2; ++i) row_pos[i] = gq + 8 * i < rows ? pos_lo + gq + 8 * i : -1;
   const int k_steps = dim >> 4, nv16 = vdim >> 4;
+  // -(score) in units of log2 e: x = S * (-scale log2 e) + c_row + slope' * (column), with the row's constant
+  // c_row = (slope (i - j0) - bias) log2 e and slope' = -slope log2 e
+  float slope_of[HPW], bias_of[HPW];
+#pragma unroll
+  for (int e = 0; e < HPW; ++e) {
+    const int h = min(warp * HPW + e, heads - 1);
+    slope_of[e] = a.slopes != nullptr ? a.slopes[h] * LOG2E : 0.f;
+    bias_of[e] = a.head_bias != nullptr ? a.head_bias[h] * LOG2E : 0.f;
+  }
 
   for (int index = begin; index < end; ++index) {
     const int stage = a.stages == 2 ? ((index - begin) & 1) : 0;
@@ -221,11 +237,7 @@ __global__ void __launch_bounds__(256) sigmoid_tiled_kernel(TiledArgs a) {
           mma_bf16(s[2 * jp + 1], qf, bfr[2], bfr[3]);
         }
       }
-      // -(score) in units of log2 e: x = S * (-scale log2 e) + c_row + slope' * (column), with the row's constant
-      // c_row = (slope (i - j0) - bias) log2 e and slope' = -slope log2 e
-      const float slope = a.slopes != nullptr ? a.slopes[h] * LOG2E : 0.f;
-      const float bias = a.head_bias != nullptr ? a.head_bias[h] * LOG2E : 0.f;
-      const float scale = -a.scale * LOG2E;
+      const float slope = slope_of[e], bias = bias_of[e], scale = -a.scale * LOG2E;
       bf16* wh = w_s + (size_t)h * W_PLANE;
       // a tile all of whose keys every row sees needs no mask
       const bool open = j0 + BN - 1 <= pos_lo && rows == BM &&
@@ -369,11 +381,13 @@ int launch(const TiledArgs& a, int warps, size_t smem, int tiles, int n_seqs, cu
                          a);
 }
 
-// Heads a warp owns: the fewest that give at most eight warps (a thread of these kernels takes up to 243 registers,
-// which is what 256 threads may have). 0: these sizes do not run here, because a warp's sums would not fit its
-// registers (heads x padded vdim above 256).
+// Heads a warp owns: the fewest that give at most eight warps (a thread of these kernels takes up to 255 registers,
+// which is what 256 threads may have); values of up to 64 take a head a warp up to sixteen warps (128 registers a
+// thread). 0: these sizes do not run here, because a warp's sums would not fit its registers (heads x padded vdim above
+// 256).
 int heads_per_warp(int heads, int vdim) {
   int padded = vdim <= 64 ? 64 : 128;
+  if (padded == 64 && heads <= 16) return 1;
   int hpw = heads <= 8 ? 1 : (heads <= 16 ? 2 : 4);
   if (hpw * padded > 256 || (heads + hpw - 1) / hpw > 8) return 0;
   return hpw;
