@@ -16,6 +16,12 @@
 // HPW - 1. (With the mixing as float32 multiply-adds out of shared memory, a head's 16 x 32 weights from all heads'
 // at 8 multiply-adds per load, a warp spent 1,000 of its 2,500 instructions a tile there and 800 on exact sigmoids.)
 //
+// Where the queries of all heads, a tile of all kv heads and all heads' weights do not fit one block's shared memory (32
+// heads of 128), a cluster of two blocks takes the 16 tokens: each block owns half the heads with their kv heads
+// (queries, keys, values and sums of its own heads only), writes the weights of its heads into BOTH blocks' shared
+// memory (`st.shared::cluster`), and mixes and sums for its own heads after a cluster barrier; a second cluster
+// barrier at the end of a tile keeps a block from writing the next tile's weights while the other still reads.
+//
 // dim and vdim: multiples of 16, at most 128 (vdim) and 256 (dim). page_size: a multiple of 32.
 #include "wide_kv.cuh"
 
@@ -58,6 +64,21 @@ __device__ __forceinline__ float sigmoid_of_exp2(float x) {
   asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(1.0f + fast_exp2(x)));
   return y;
 }
+__device__ __forceinline__ unsigned cluster_rank() {
+  unsigned r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Four bytes to the same shared-memory place in block `rank` of the cluster.
+__device__ __forceinline__ void store_remote(const void* local, unsigned rank, unsigned value) {
+  unsigned addr = (unsigned)__cvta_generic_to_shared(local), remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(addr), "r"(rank));
+  asm volatile("st.shared::cluster.b32 [%0], %1;" ::"r"(remote), "r"(value) : "memory");
+}
 __device__ __forceinline__ float sigmoid_exact(float g) {
   if (g >= 0.f) return 1.0f / (1.0f + expf(-g));
   float e = expf(g);
@@ -76,6 +97,7 @@ struct TiledArgs {
   float* part;          // splits > 1: [split][token][heads * vdim] float32 sums, no gate (sigmoid_combine finishes)
   int splits, tokens;   // blocks that share a block's tiles of keys (blockIdx.z); the step's tokens
   int heads, window, keep, stages;
+  int cluster;          // blocks that share a block of 16 tokens, each with its share of the heads (1 or 2)
   float scale;
   const int* cu_seqlens;
   const int* tok_pos;
@@ -85,15 +107,21 @@ struct TiledArgs {
 template <int HPW, int VD>
 __global__ void __launch_bounds__(HPW == 1 && VD == 64 ? 512 : 256) sigmoid_tiled_kernel(TiledArgs a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  const int heads = a.heads, groups = a.cache.kv_heads, share = heads / groups;
+  // `all_heads` is the model's; heads, groups: this block's own (all of them, or its half in a cluster of two), which
+  // start at head h0 and kv head g0
+  const int all_heads = a.heads, share = all_heads / a.cache.kv_heads;
+  const unsigned crank = a.cluster > 1 ? cluster_rank() : 0;
+  const int heads = all_heads / a.cluster, groups = a.cache.kv_heads / a.cluster;
+  const int h0 = (int)crank * heads, g0 = (int)crank * groups;
   const int dim = a.cache.key_dim, vdim = a.cache.value_dim;
   const int k_ld = dim + 8, v_ld = vdim + 8;
   bf16* q_s = reinterpret_cast<bf16*>(smem_raw);                 // [heads][BM][k_ld]
   bf16* k_s = q_s + (size_t)heads * BM * k_ld;                   // [stages][groups][BN][k_ld]
   bf16* v_s = k_s + (size_t)a.stages * groups * BN * k_ld;       // [stages][groups][BN][v_ld]
-  const int head_tiles = (heads + 15) >> 4;
-  bf16* w_s = v_s + (size_t)a.stages * groups * BN * v_ld;       // [16 head_tiles][W_PLANE]: weights before the mixing
-  bf16* p_s = a.mix != nullptr ? w_s + (size_t)head_tiles * 16 * W_PLANE : w_s;  // ... and after it (or the same)
+  const int head_tiles = (all_heads + 15) >> 4, own_tiles = (heads + 15) >> 4;
+  bf16* w_s = v_s + (size_t)a.stages * groups * BN * v_ld;       // [16 head_tiles][W_PLANE]: ALL heads' weights
+  // ... and this block's heads' weights after the mixing (without a mixing matrix: its own planes of w_s)
+  bf16* p_s = a.mix != nullptr ? w_s + (size_t)head_tiles * 16 * W_PLANE : w_s + (size_t)h0 * W_PLANE;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, threads = blockDim.x, warps = threads >> 5;
   const int gq = lane >> 2, tq = lane & 3, mat = lane >> 3;
   pdl_launch_dependents();
@@ -106,20 +134,20 @@ __global__ void __launch_bounds__(HPW == 1 && VD == 64 ? 512 : 256) sigmoid_tile
       for (int kt = 0; kt < MAX_HEAD_TILES; ++kt)
 #pragma unroll
         for (int x = 0; x < 4; ++x) {
-          int h = mt * 16 + gq + 8 * (x & 1), g = kt * 16 + tq * 2 + 8 * (x >> 1);
-          float lo = h < heads && g < heads ? a.mix[h * heads + g] : 0.f;
-          float hi = h < heads && g + 1 < heads ? a.mix[h * heads + g + 1] : 0.f;
+          int h = mt * 16 + gq + 8 * (x & 1), g = kt * 16 + tq * 2 + 8 * (x >> 1);  // (h: among this block's heads)
+          float lo = h < heads && g < all_heads ? a.mix[(h0 + h) * all_heads + g] : 0.f;
+          float hi = h < heads && g + 1 < all_heads ? a.mix[(h0 + h) * all_heads + g + 1] : 0.f;
           m_frag[mt][kt][x] = pack_bf16(lo, hi);
         }
     // heads beyond the model's (the padding of the last tile of 16) have weights of zero for good
-    for (int i = tid; i < (head_tiles * 16 - heads) * W_PLANE; i += threads)
-      w_s[(size_t)heads * W_PLANE + i] = __float2bfloat16_rn(0.f);
+    for (int i = tid; i < (head_tiles * 16 - all_heads) * W_PLANE; i += threads)
+      w_s[(size_t)all_heads * W_PLANE + i] = __float2bfloat16_rn(0.f);
   }
   pdl_wait();
   const int b = blockIdx.y;
   const int tok0 = a.cu_seqlens[b], n_new = a.cu_seqlens[b + 1] - tok0;
   // (the last tokens of a sequence see the most keys: they go first)
-  const int m0 = (gridDim.x - 1 - blockIdx.x) * BM;
+  const int m0 = (gridDim.x / a.cluster - 1 - blockIdx.x / a.cluster) * BM;
   if (m0 >= n_new) return;
   const int rows = min(BM, n_new - m0);
   const int pos_lo = a.tok_pos[tok0] + m0, pos_hi = pos_lo + rows - 1;  // positions of new tokens are consecutive
@@ -138,10 +166,10 @@ __global__ void __launch_bounds__(HPW == 1 && VD == 64 ? 512 : 256) sigmoid_tile
     const int per = (count + a.splits - 1) / a.splits;
     begin = blockIdx.z * per;
     end = min(count, begin + per);
-    if (begin >= end) {  // nothing left for this block: its rows' sums are zeros
-      const int outputs = heads * vdim;
-      for (int i = tid; i < rows * outputs; i += threads)
-        a.part[((size_t)blockIdx.z * a.tokens + tok0 + m0 + i / outputs) * outputs + i % outputs] = 0.f;
+    if (begin >= end) {  // nothing left for this block: its heads' sums of its rows are zeros
+      const int outputs = all_heads * vdim, mine = heads * vdim;
+      for (int i = tid; i < rows * mine; i += threads)
+        a.part[((size_t)blockIdx.z * a.tokens + tok0 + m0 + i / mine) * outputs + h0 * vdim + i % mine] = 0.f;
       return;
     }
   }
@@ -163,10 +191,10 @@ __global__ void __launch_bounds__(HPW == 1 && VD == 64 ? 512 : 256) sigmoid_tile
   auto load_tile = [&](int stage, int index) {
     const int j0 = first_key(index);
     const int page = pages[j0 / a.cache.page_size], row0 = j0 % a.cache.page_size;
-    load_rows(k_s + (size_t)stage * groups * BN * k_ld, k_ld, k_pieces, k_shift, dim, key_at(a.cache, page, 0, row0),
+    load_rows(k_s + (size_t)stage * groups * BN * k_ld, k_ld, k_pieces, k_shift, dim, key_at(a.cache, page, g0, row0),
               (size_t)a.cache.page_size * dim);
     load_rows(v_s + (size_t)stage * groups * BN * v_ld, v_ld, v_pieces, v_shift, vdim,
-              value_at(a.cache, page, 0, row0), (size_t)a.cache.page_size * vdim);
+              value_at(a.cache, page, g0, row0), (size_t)a.cache.page_size * vdim);
   };
   load_tile(0, begin);
   cp_async_commit();
@@ -175,7 +203,8 @@ __global__ void __launch_bounds__(HPW == 1 && VD == 64 ? 512 : 256) sigmoid_tile
   for (int idx = tid; idx < heads * BM * k_pieces; idx += threads) {
     int h = idx / (BM * k_pieces), rest = idx - h * BM * k_pieces, r = rest / k_pieces, c = rest - r * k_pieces;
     uint4 v = make_uint4(0, 0, 0, 0);
-    if (r < rows) v = *reinterpret_cast<const uint4*>(a.q + ((size_t)(tok0 + m0 + r) * heads + h) * dim + c * 8);
+    if (r < rows)
+      v = *reinterpret_cast<const uint4*>(a.q + ((size_t)(tok0 + m0 + r) * all_heads + h0 + h) * dim + c * 8);
     *reinterpret_cast<uint4*>(q_s + ((size_t)h * BM + r) * k_ld + c * 8) = v;
   }
 
@@ -195,10 +224,11 @@ __global__ void __launch_bounds__(HPW == 1 && VD == 64 ? 512 : 256) sigmoid_tile
   float slope_of[HPW], bias_of[HPW];
 #pragma unroll
   for (int e = 0; e < HPW; ++e) {
-    const int h = min(warp * HPW + e, heads - 1);
+    const int h = h0 + min(warp * HPW + e, heads - 1);
     slope_of[e] = a.slopes != nullptr ? a.slopes[h] * LOG2E : 0.f;
     bias_of[e] = a.head_bias != nullptr ? a.head_bias[h] * LOG2E : 0.f;
   }
+  if (a.cluster > 1) cluster_sync();  // (the other block runs, and has cleared its padding, before anyone writes to it)
 
   for (int index = begin; index < end; ++index) {
     const int stage = a.stages == 2 ? ((index - begin) & 1) : 0;
@@ -238,7 +268,7 @@ __global__ void __launch_bounds__(HPW == 1 && VD == 64 ? 512 : 256) sigmoid_tile
         }
       }
       const float slope = slope_of[e], bias = bias_of[e], scale = -a.scale * LOG2E;
-      bf16* wh = w_s + (size_t)h * W_PLANE;
+      bf16* wh = w_s + (size_t)(h0 + h) * W_PLANE;
       // a tile all of whose keys every row sees needs no mask
       const bool open = j0 + BN - 1 <= pos_lo && rows == BM &&
                         (a.window <= 0 || pos_hi - j0 < a.window || j0 + BN <= a.keep);
@@ -257,11 +287,14 @@ __global__ void __launch_bounds__(HPW == 1 && VD == 64 ? 512 : 256) sigmoid_tile
               if (!(key <= i && (a.window <= 0 || i - key < a.window || key < a.keep))) w[c] = 0.f;
             }
           }
-          *reinterpret_cast<unsigned*>(wh + (size_t)(gq + 8 * half) * W_LD + j * 8 + tq * 2) = pack_bf16(w[0], w[1]);
+          bf16* at = wh + (size_t)(gq + 8 * half) * W_LD + j * 8 + tq * 2;
+          const unsigned both = pack_bf16(w[0], w[1]);
+          *reinterpret_cast<unsigned*>(at) = both;
+          if (a.cluster > 1) store_remote(at, crank ^ 1, both);
         }
       }
     }
-    __syncthreads();
+    if (a.cluster > 1) cluster_sync(); else __syncthreads();
     // 3. the mixing as a product: P[h][pair] = sum_g M[h][g] W[g][pair], pairs = the tile's (query, key) places; a warp
     // takes every warps-th stretch of 16 keys of a query row
     if (a.mix != nullptr) {
@@ -282,7 +315,7 @@ __global__ void __launch_bounds__(HPW == 1 && VD == 64 ? 512 : 256) sigmoid_tile
                                        (mat >> 1) * 8);
 #pragma unroll
             for (int mt = 0; mt < MAX_HEAD_TILES; ++mt) {
-              if (mt < head_tiles) {
+              if (mt < own_tiles) {
                 mma_bf16(d[mt][0], m_frag[mt][kt], bfr[0], bfr[1]);
                 mma_bf16(d[mt][1], m_frag[mt][kt], bfr[2], bfr[3]);
               }
@@ -296,7 +329,7 @@ __global__ void __launch_bounds__(HPW == 1 && VD == 64 ? 512 : 256) sigmoid_tile
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
               const int h = mt * 16 + gq + 8 * half;
-              if (mt < head_tiles && h < heads)
+              if (mt < own_tiles && h < heads)
                 *reinterpret_cast<unsigned*>(p_s + (size_t)h * W_PLANE + row * W_LD + col + n * 8 + tq * 2) =
                     pack_bf16(d[mt][n][half * 2], d[mt][n][half * 2 + 1]);
             }
@@ -325,7 +358,8 @@ __global__ void __launch_bounds__(HPW == 1 && VD == 64 ? 512 : 256) sigmoid_tile
         }
       }
     }
-    __syncthreads();  // the tile's stage and the weights are free again
+    // the tile's stage and the weights are free again (in a cluster: also for the other block's next weights)
+    if (a.cluster > 1) cluster_sync(); else __syncthreads();
     if (a.stages == 1 && index + 1 < end) {
       load_tile(0, index + 1);
       cp_async_commit();
@@ -345,10 +379,11 @@ __global__ void __launch_bounds__(HPW == 1 && VD == 64 ? 512 : 256) sigmoid_tile
       for (int i = 0; i < VD / 8; ++i) {
         const int d = i * 8 + tq * 2;
         if (d >= vdim) continue;
-        const size_t o = (size_t)h * vdim + d;
+        const size_t o = (size_t)(h0 + h) * vdim + d;
         float x = o_acc[e][i][half * 2], y = o_acc[e][i][half * 2 + 1];
         if (a.splits > 1) {
-          *reinterpret_cast<float2*>(a.part + ((size_t)blockIdx.z * a.tokens + t) * heads * vdim + o) = make_float2(x, y);
+          *reinterpret_cast<float2*>(a.part + ((size_t)blockIdx.z * a.tokens + t) * all_heads * vdim + o) =
+              make_float2(x, y);
           continue;
         }
         if (a.gates != nullptr) {
@@ -356,16 +391,19 @@ __global__ void __launch_bounds__(HPW == 1 && VD == 64 ? 512 : 256) sigmoid_tile
           x *= sigmoid_exact(z.x);
           y *= sigmoid_exact(z.y);
         }
-        *reinterpret_cast<__nv_bfloat162*>(a.out + t * heads * vdim + o) = __floats2bfloat162_rn(x, y);
+        *reinterpret_cast<__nv_bfloat162*>(a.out + t * all_heads * vdim + o) = __floats2bfloat162_rn(x, y);
       }
     }
   }
 }
 
-size_t shared_bytes(int heads, int groups, int dim, int vdim, int stages, bool mixes = true) {
-  size_t planes = (size_t)((heads + 15) / 16) * 16 * (mixes ? 2 : 1);
-  return ((size_t)heads * BM * (dim + 8) + (size_t)stages * groups * BN * (dim + 8 + vdim + 8) + planes * W_PLANE) *
-         sizeof(bf16);
+// A block's shared memory: the queries of its `heads` (all of them, or half in a cluster of two), `stages` tiles of
+// its kv heads, the weights of ALL heads and its own heads' mixed weights.
+size_t shared_bytes(int all_heads, int groups, int dim, int vdim, int stages, int cluster) {
+  int heads = all_heads / cluster;
+  size_t planes = (size_t)((all_heads + 15) / 16) * 16 + (size_t)((heads + 15) / 16) * 16;
+  return ((size_t)heads * BM * (dim + 8) + (size_t)stages * (groups / cluster) * BN * (dim + 8 + vdim + 8) +
+          planes * W_PLANE) * sizeof(bf16);
 }
 
 template <int HPW, int VD>
@@ -377,20 +415,47 @@ int launch(const TiledArgs& a, int warps, size_t smem, int tiles, int n_seqs, cu
       return DLLM_LAUNCH_FAILED;
     configured = smem;
   }
-  return dllm_launch_pdl(sigmoid_tiled_kernel<HPW, VD>, dim3(tiles, n_seqs, a.splits), dim3(warps * 32), smem, stream,
-                         a);
+  if (a.cluster == 1)
+    return dllm_launch_pdl(sigmoid_tiled_kernel<HPW, VD>, dim3(tiles, n_seqs, a.splits), dim3(warps * 32), smem,
+                           stream, a);
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(tiles * a.cluster, n_seqs, a.splits);
+  config.blockDim = dim3(warps * 32);
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attributes[2];
+  attributes[0].id = cudaLaunchAttributeClusterDimension;
+  attributes[0].val.clusterDim.x = a.cluster;
+  attributes[0].val.clusterDim.y = 1;
+  attributes[0].val.clusterDim.z = 1;
+  attributes[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attributes[1].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attributes;
+  config.numAttrs = dllm_pdl_enabled() ? 2 : 1;
+  return cudaLaunchKernelEx(&config, sigmoid_tiled_kernel<HPW, VD>, a) == cudaSuccess ? DLLM_OK : DLLM_LAUNCH_FAILED;
 }
 
-// Heads a warp owns: the fewest that give at most eight warps (a thread of these kernels takes up to 255 registers,
-// which is what 256 threads may have); values of up to 64 take a head a warp up to sixteen warps (128 registers a
-// thread). 0: these sizes do not run here, because a warp's sums would not fit its registers (heads x padded vdim above
-// 256).
+// Heads a warp owns, of a block's `heads`: the fewest that give at most eight warps (a thread of these kernels takes
+// up to 255 registers, which is what 256 threads may have); values of up to 64 take a head a warp up to sixteen warps
+// (128 registers a thread). 0: these sizes do not run here, because a warp's sums would not fit its registers (heads x
+// padded vdim above 256).
 int heads_per_warp(int heads, int vdim) {
   int padded = vdim <= 64 ? 64 : 128;
   if (padded == 64 && heads <= 16) return 1;
   int hpw = heads <= 8 ? 1 : (heads <= 16 ? 2 : 4);
   if (hpw * padded > 256 || (heads + hpw - 1) / hpw > 8) return 0;
   return hpw;
+}
+
+// Blocks that share 16 tokens: 1 where one block holds everything, 2 where two halves of the heads do (whole tiles of
+// 16 heads and whole kv heads each), 0 where neither does.
+int blocks_for(int heads, int kv_heads, int dim, int vdim) {
+  if (heads > 16 * MAX_HEAD_TILES) return 0;
+  if (heads_per_warp(heads, vdim) != 0 && shared_bytes(heads, kv_heads, dim, vdim, 1, 1) <= 220 * 1024) return 1;
+  if (heads % 32 == 0 && kv_heads % 2 == 0 && (heads / 2) % (heads / kv_heads) == 0 &&
+      heads_per_warp(heads / 2, vdim) != 0 && shared_bytes(heads, kv_heads, dim, vdim, 1, 2) <= 220 * 1024)
+    return 2;
+  return 0;
 }
 }  // namespace
 
@@ -399,8 +464,7 @@ DLLM_EXPORT int dllm_sigmoid_attention_tiled_fits(int heads, int kv_heads, int d
   if (heads <= 0 || kv_heads <= 0 || heads % kv_heads || dim <= 0 || dim > 256 || (dim & 15) || vdim <= 0 ||
       vdim > 128 || (vdim & 15) || page_size <= 0 || page_size % BN)
     return 0;
-  if (heads_per_warp(heads, vdim) == 0 || heads > 16 * MAX_HEAD_TILES) return 0;
-  return shared_bytes(heads, kv_heads, dim, vdim, 1) <= 220 * 1024 ? 1 : 0;
+  return blocks_for(heads, kv_heads, dim, vdim) != 0 ? 1 : 0;
 }
 
 // max_new: the most new tokens any sequence of the step has (the grid covers that many for every sequence; blocks
@@ -420,15 +484,16 @@ DLLM_EXPORT int dllm_sigmoid_attention_tiled(const void* q, void* out, const voi
     return DLLM_UNSUPPORTED_SIZE;
   if (!q || !out || !cache_base || !page_table || !cu_seqlens || !tok_pos || !slots) return DLLM_BAD_ARGUMENT;
   if (splits < 1 || splits > 65535 || (splits > 1 && (!part || tokens <= 0))) return DLLM_BAD_ARGUMENT;
-  int stages = shared_bytes(heads, kv_heads, dim, vdim, 2) <= 110 * 1024 ? 2 : 1;
-  if (stages == 1 && shared_bytes(heads, kv_heads, dim, vdim, 2) <= 220 * 1024 &&
-      shared_bytes(heads, kv_heads, dim, vdim, 1) > 110 * 1024)
-    stages = 2;  // (one block a multiprocessor either way: the second stage costs nothing)
+  int cluster = blocks_for(heads, kv_heads, dim, vdim);
+  // two stages where two blocks a multiprocessor still fit, or where only one fits either way
+  size_t one = shared_bytes(heads, kv_heads, dim, vdim, 1, cluster), two = shared_bytes(heads, kv_heads, dim, vdim, 2, cluster);
+  int stages = (two <= 110 * 1024 || (two <= 220 * 1024 && one > 110 * 1024)) ? 2 : 1;
   TiledArgs a{(const bf16*)q, WideKv{(void*)cache_base, page_table, max_pages, page_size, kv_heads, dim, vdim}, mix,
-              slopes, head_bias, gates, gate_ld, (bf16*)out, part, splits, tokens, heads, window, keep, stages, scale,
-              cu_seqlens, tok_pos, slots};
-  size_t smem = shared_bytes(heads, kv_heads, dim, vdim, stages);
-  int hpw = heads_per_warp(heads, vdim), warps = (heads + hpw - 1) / hpw;
+              slopes, head_bias, gates, gate_ld, (bf16*)out, part, splits, tokens, heads, window, keep, stages, cluster,
+              scale, cu_seqlens, tok_pos, slots};
+  size_t smem = stages == 2 ? two : one;
+  int own = heads / cluster;
+  int hpw = heads_per_warp(own, vdim), warps = (own + hpw - 1) / hpw;
   int tiles = (max_new + BM - 1) / BM;
   bool narrow = vdim <= 64;
   if (hpw == 1) return narrow ? launch<1, 64>(a, warps, smem, tiles, n_seqs, stream)

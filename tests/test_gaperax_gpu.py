@@ -269,6 +269,9 @@ ATTENTION_SHAPES = {
     "all_seen": _attention_shape(3, 1, 20, 24, 500, 0, scale=0.15),
     "kept_beyond_the_window": _attention_shape(2, 2, 64, 64, 16, 100, scale=0.08),
     "many_heads": _attention_shape(24, 8, 16, 40, 33, 31),
+    # (queries, a tile and the weights of 32 heads of 128 do not fit one block: two blocks of a cluster share them)
+    "two_blocks": _attention_shape(32, 8, 128, 128, 90, 10, scale=0.05),
+    "two_blocks_two_kv_heads": _attention_shape(32, 2, 112, 96, 40, 70, scale=0.05),
 }
 
 
