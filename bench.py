@@ -1015,13 +1015,13 @@ def revupel_rooflines(row: dict, size: dict, batch: int, peak: dict, contexts: l
 def gaperax_config(size: dict) -> dict:
     """A Gaperax model of `size`: latent attention and windowed sigmoid attention in turn (the latent as the Revupel
     model's: twice a head wide, at most 256, a shared rotated part of half a head, a query latent of three eighths of
-    the width, frequencies stretched four times beyond 2,048 positions), a window of 1,024 positions that keeps the
+    the width, frequencies stretched eight times beyond 4,096 positions), a window of 1,024 positions that keeps the
     first 64, keys and values of a head's size, the dense gated feed-forward of the Llama model's width."""
     h, g, d, width = size["heads"], size["kv_heads"], size["dim"], size["width"]
     latent = {"heads": h, "dim": d, "rot_dim": d // 2, "vdim": d, "q_rank": 3 * width // 8, "kv_rank": min(2 * d, 256),
               "scale": (d + d // 2) ** -0.5,
               "rot": {"base": 500000.0, "dims": d // 2,
-                      "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}
+                      "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
     attention = {"heads": h, "kv_heads": g, "dim": d, "vdim": d, "scale": d ** -0.5,
                  "mask": {"size": GAPERAX_WINDOW, "keep_first": GAPERAX_KEPT}}
     mlp = {"kind": "dense", "ff": size["ff"]}
