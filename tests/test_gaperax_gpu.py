@@ -321,7 +321,7 @@ def test_one_marked_value_shows_exactly_where_it_is_seen(name, dtype, size, keep
     seen = [i for i in range(n) if i >= marked and (i - marked < size or marked < keep_first)]
     unseen = [i for i in range(n) if i not in seen]
     moved = np.abs(want - without).max(axis=1) / np.abs(without).max()
-    assert all(moved[i] > 0.5 for i in seen) and all(moved[i] == 0 for i in unseen)  # the test's premise
+    assert all(moved[i] > 0.2 for i in seen) and all(moved[i] == 0 for i in unseen)  # the test's premise
     assert seen and (marked < keep_first or unseen[-1] > marked)
     assert rel_error(got, want) <= PART_TOL[dtype]
     # the rows that do not see the mark equal the run without it, to rounding of their own sums
